@@ -1,0 +1,77 @@
+// Shared helpers for the sm_100a kernels: element types, conversions, reductions.
+//
+// Every launcher is `extern "C"`, takes raw device pointers, sizes and a stream,
+// and returns the cudaError_t of its launch as an int (0 = ok).  Element types
+// are passed as codes: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define MLS_F32 0
+#define MLS_BF16 1
+
+#define MLS_API extern "C" __attribute__((visibility("default")))
+
+// Error codes a launcher may return besides a cudaError_t.
+#define MLS_ERR_UNSUPPORTED 100001   // a size this kernel refuses
+
+// Bits of the device status word (set by kernels, read by the host).
+#define MLS_STATUS_BAD_TOKEN 1       // token id outside the vocabulary
+#define MLS_STATUS_BAD_POSITION 2    // position outside the rotary table
+#define MLS_STATUS_BAD_SLOT 4        // a slot or page index outside the pool
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) {
+        return __bfloat162float(*p);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) {
+        *p = __float2bfloat16_rn(v);
+    }
+};
+
+static __device__ __forceinline__ float load_as_float(const void* base, size_t i, int dtype) {
+    return dtype == MLS_BF16 ? __bfloat162float(((const __nv_bfloat16*)base)[i])
+                             : ((const float*)base)[i];
+}
+static __device__ __forceinline__ void store_from_float(void* base, size_t i, int dtype, float v) {
+    if (dtype == MLS_BF16) ((__nv_bfloat16*)base)[i] = __float2bfloat16_rn(v);
+    else ((float*)base)[i] = v;
+}
+
+static __device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+static __device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of the additions depends only on blockDim, never on the data or on what
+// else runs, so a row's result does not depend on the batch it is in.
+static __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+static inline int launch_status() { return (int)cudaGetLastError(); }

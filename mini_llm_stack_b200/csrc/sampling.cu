@@ -1,0 +1,93 @@
+// Sampling over float32 logits [n, V].
+//
+// Greedy: the reference takes logits.argmax(-1) (serve/engine.py:187-188); ties go
+// to the lowest index.  Temperature: the reference draws from
+// softmax(logits / temperature) (train/model.py:262-264).  Here the draw is an
+// inverse-CDF lookup with a uniform number u given by the host: the token is
+// the first index whose cumulative probability exceeds u, in vocabulary order,
+// so the same (logits, temperature, u) always gives the same token.  A row whose
+// temperature is <= 0 is taken greedily.
+#include "common.cuh"
+
+namespace {
+constexpr int THREADS = 256;
+constexpr int NONE = 0x7fffffff;
+
+__device__ __forceinline__ int block_argmax(const float* row, int vocab, float scale,
+                                            float* vs, int* is) {
+    float best = -INFINITY;
+    int idx = NONE;
+    for (int i = threadIdx.x; i < vocab; i += THREADS) {
+        const float v = row[i] * scale;
+        if (v > best || (idx == NONE && v == best)) { best = v; idx = i; }
+    }
+    vs[threadIdx.x] = best;
+    is[threadIdx.x] = idx;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float v2 = vs[threadIdx.x + s];
+            const int i2 = is[threadIdx.x + s];
+            if (v2 > vs[threadIdx.x] || (v2 == vs[threadIdx.x] && i2 < is[threadIdx.x])) {
+                vs[threadIdx.x] = v2;
+                is[threadIdx.x] = i2;
+            }
+        }
+        __syncthreads();
+    }
+    return is[0] == NONE ? 0 : is[0];
+}
+
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+              const float* __restrict__ uniform, int* __restrict__ out, int vocab) {
+    __shared__ float vs[THREADS];
+    __shared__ int is[THREADS];
+    __shared__ float scratch[33];
+    __shared__ int cand;
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const float temp = temperature ? temperature[blockIdx.x] : 0.f;
+    if (!(temp > 0.f)) {
+        const int tok = block_argmax(row, vocab, 1.0f, vs, is);
+        if (threadIdx.x == 0) out[blockIdx.x] = tok;
+        return;
+    }
+    const float inv_t = 1.0f / temp;
+    const int top = block_argmax(row, vocab, inv_t, vs, is);
+    const float mx = row[top] * inv_t;
+
+    float part = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += THREADS) part += expf(row[i] * inv_t - mx);
+    const float total = block_sum(part, scratch);
+    const float target = uniform[blockIdx.x] * total;
+
+    float running = 0.f;
+    int found = -1;
+    for (int base = 0; base < vocab && found < 0; base += THREADS) {
+        const int i = base + threadIdx.x;
+        if (threadIdx.x == 0) cand = NONE;
+        vs[threadIdx.x] = i < vocab ? expf(row[i] * inv_t - mx) : 0.f;
+        __syncthreads();
+        for (int off = 1; off < THREADS; off <<= 1) {       // inclusive scan of the chunk
+            const float add = threadIdx.x >= off ? vs[threadIdx.x - off] : 0.f;
+            __syncthreads();
+            vs[threadIdx.x] += add;
+            __syncthreads();
+        }
+        if (i < vocab && running + vs[threadIdx.x] > target) atomicMin(&cand, i);
+        __syncthreads();
+        if (cand != NONE) found = cand;
+        running += vs[THREADS - 1];
+        __syncthreads();
+    }
+    // u * total may round past the last cumulative sum: the last token then
+    if (threadIdx.x == 0) out[blockIdx.x] = found < 0 ? vocab - 1 : found;
+}
+}  // namespace
+
+MLS_API int mls_sample(const float* logits, const float* temperature, const float* uniform,
+                       int* out, int n_rows, int vocab, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, temperature, uniform, out, vocab);
+    return launch_status();
+}

@@ -1,0 +1,120 @@
+"""The step function: run a batch of (request, next tokens) from the cache.
+
+The reference has two runner calls: ``prefill`` for one whole prompt alone
+(serve/engine.py:76-105) and ``decode_step`` for n sequences of one token each
+(serve/engine.py:107-157); both follow the order norm -> q,k,v -> RoPE -> write
+K/V -> attend -> wo + residual -> norm -> mlp + residual and advance the
+lengths once after the last layer (serve/engine.py:103,155-156).  Only
+``CachedModel.logits_for`` (serve/speculative.py:53-68) feeds a portion of a
+sequence against cached context.  Here there is one ``step``: any mix of
+portions (from two tokens up to a whole prompt) and single decoded tokens runs
+as one batch and returns float32 logits at the wanted places only.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import CacheError, CacheManager
+from ..config.registry import build_model, config_from_folder
+from ..ops.kernels import Runtime
+from ..weights.loader import device_dtype, load_tensors
+from ..weights.random_init import random_tensors
+from .batch import BatchBuilder, Entry
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def load_model(folder, dtype: str | None = None, device="cuda:0"):
+    """Model of a folder (config.json + model.safetensors), bound to a runtime."""
+    config = config_from_folder(folder)
+    run_dtype = _TORCH_DTYPES[dtype or config.dtype]
+    runtime = Runtime(device, run_dtype)
+    model = build_model(config)
+    tensors = load_tensors(folder, model.tensor_specs(), model.tied_names(), run_dtype,
+                           runtime.device)
+    model.bind(tensors, runtime)
+    return model
+
+
+def random_model(config, seed: int, norm_std: float = 0.0, dtype: str | None = None,
+                 device="cuda:0", fast: bool = False):
+    """Model with random weights, without a folder in between.
+
+    The tensors are those ``write_random_model`` would store for the same
+    (config, seed, norm_std).  ``fast`` draws them on the device instead (other
+    values, same distribution): a billion-parameter model is then ready in
+    seconds, for measurements.
+    """
+    from ..weights.random_init import INIT_STD
+    run_dtype = _TORCH_DTYPES[dtype or config.dtype]
+    runtime = Runtime(device, run_dtype)
+    model = build_model(config)
+    tensors = {}
+    if fast:
+        gen = torch.Generator(device=runtime.device).manual_seed(int(seed))
+        for name, spec in model.tensor_specs().items():
+            if spec.init == "normal":
+                t = torch.empty(spec.shape, dtype=run_dtype, device=runtime.device)
+                t.normal_(0.0, INIT_STD, generator=gen)
+            else:
+                t = torch.ones(spec.shape, dtype=run_dtype, device=runtime.device)
+                if spec.init == "zeros":
+                    t.zero_()
+            tensors[name] = t
+    else:
+        specs = model.tensor_specs()
+        for name, t in random_tensors(config, seed, norm_std):
+            # what a folder would hold, then what a load would make of it
+            tensors[name] = t.to(device=runtime.device,
+                                 dtype=device_dtype(t.dtype, specs[name].kind, run_dtype))
+    model.bind(tensors, runtime)
+    return model
+
+
+class ModelRunner:
+    """A bound model, its cache and the step function over both."""
+
+    def __init__(self, model, num_blocks: int, block_size: int = 16, max_requests: int = 16):
+        self.model = model
+        self.runtime = model.runtime
+        cfg = model.config
+        self.cache = CacheManager(
+            model.cache_specs(), num_blocks=num_blocks, block_size=block_size,
+            max_requests=max_requests, max_seq_len=cfg.max_seq_len,
+            device=self.runtime.device, kv_dtype=self.runtime.act_dtype)
+        self.handles = self.cache.handles()
+        self.builder = BatchBuilder(self.cache, self.runtime.device, cfg.vocab_size,
+                                    cfg.max_seq_len)
+        self.steps = 0
+
+    def reserve(self, entries: list) -> None:
+        """Pages for every entry's tokens; ``CacheError`` when they run out
+        (entries before the failing one keep what they were given)."""
+        for e in entries:
+            if not self.cache.has(e.owner):
+                if not self.cache.admit(e.owner):
+                    raise CacheError("no state slot is free for a new request")
+            if not self.cache.reserve(e.owner, len(e.tokens)):
+                raise CacheError(
+                    f"out of cache pages: request {e.owner!r} needs room for "
+                    f"{len(e.tokens)} more tokens, {self.cache.num_free_pages()} pages free")
+
+    @torch.no_grad()
+    def step(self, entries: list):
+        """Run the entries' tokens as one batch; float32 logits [n_out, vocab].
+
+        Pages for the tokens must be reserved.  Keys and values of the tokens
+        are written into the cache layer by layer before that layer attends;
+        the requests' lengths advance once, after the last layer.
+        """
+        ctx = self.builder.build(entries)
+        logits = self.model.forward(ctx, self.handles)
+        for e in entries:
+            self.cache.commit(e.owner, len(e.tokens))
+        self.steps += 1
+        return logits
+
+    def release(self, owner) -> None:
+        if self.cache.has(owner):
+            self.cache.free(owner)

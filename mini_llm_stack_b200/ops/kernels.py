@@ -1,0 +1,257 @@
+"""Python faces of the CUDA kernels, and the runtime the parts run on.
+
+Each method checks shapes and types on the host, then calls one exported C
+launcher with raw device pointers on torch's current stream.  Nothing here
+computes on the CPU and nothing falls back to a library implementation of a
+part of the model; the only library call is the plain bfloat16 matrix product
+where the own kernel does not apply (the reference multiplies with
+``nn.Linear``, i.e. a library GEMM: train/model.py:79-82,130-132,227).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import library
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_F = ctypes.c_float
+_LL = ctypes.c_longlong
+
+_ERRORS = {100001: "a size this kernel does not support"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        why = _ERRORS.get(rc)
+        if why is None:
+            why = f"CUDA error {rc}"
+        raise KernelError(f"{what}: {why}")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _decl(lib, name, argtypes):
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = ctypes.c_int
+    return fn
+
+
+class Ops:
+    """The kernels, bound to one device.  Fails at construction without a GPU."""
+
+    def __init__(self, device, act_dtype: torch.dtype):
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelError(
+                "this engine runs on a CUDA device only (sm_100a kernels); "
+                f"device {device!r} is not one and there is no CPU path")
+        self.act_dtype = act_dtype
+        core = library.load("core")
+        self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _P, _P])
+        self._add_rmsnorm = _decl(core, "mls_add_rmsnorm",
+                                  [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _P])
+        self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _P, _P, _I, _I, _I, _P])
+        self._rope_store = _decl(core, "mls_rope_store",
+                                 [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                                  _LL, _I, _P, _P])
+        self._attention_simt = _decl(core, "mls_attention_simt",
+                                     [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
+                                      _I, _F, _I, _P])
+        self._swiglu = _decl(core, "mls_swiglu", [_P, _P, _I, _I, _I, _P])
+        self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P])
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._attention_libs: dict = {}
+        self._gemm = None
+        self.attention_impl = os.environ.get("MLS_B200_ATTENTION", "auto")
+        self.gemm_impl = os.environ.get("MLS_B200_GEMM", "auto")
+        self.launches = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def check_status(self) -> None:
+        """Raise if a kernel met a token, position or slot outside its table."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            what = [n for b, n in ((1, "a token id outside the vocabulary"),
+                                   (2, "a position outside the rotary table"),
+                                   (4, "a cache slot outside the pool")) if code & b]
+            raise KernelError("a kernel refused its input: " + "; ".join(what))
+
+    # ------------------------------------------------------------------ kernels
+    def embed(self, token_ids, table, x, vocab: int) -> None:
+        t, d = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "embed: x must be float32")
+        _need(table.shape == (vocab, d) and table.is_contiguous(), "embed: bad table")
+        _need(token_ids.dtype == torch.int32 and token_ids.numel() >= t, "embed: bad ids")
+        self.launches += 1
+        _check(self._embed(_ptr(token_ids), _ptr(table), _code(table.dtype), _ptr(x), t, d,
+                           vocab, _ptr(self.status), self._stream()), "embed")
+
+    def add_rmsnorm(self, x, delta, weight, eps: float, h) -> None:
+        t, d = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "add_rmsnorm: x must be float32")
+        _need(h.shape == (t, d) and h.is_contiguous(), "add_rmsnorm: bad output")
+        _need(weight.shape == (d,), "add_rmsnorm: bad weight")
+        if delta is not None:
+            _need(delta.shape == (t, d) and delta.is_contiguous(), "add_rmsnorm: bad delta")
+        self.launches += 1
+        _check(self._add_rmsnorm(_ptr(x), _ptr(delta),
+                                 _code(delta.dtype) if delta is not None else 0,
+                                 _ptr(weight), _code(weight.dtype), float(eps), _ptr(h),
+                                 _code(h.dtype), t, d, None, self._stream()), "add_rmsnorm")
+
+    def gather_add_rmsnorm(self, x, delta, rows, n_rows: int, weight, eps: float, h) -> None:
+        t, d = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "gather_add_rmsnorm: bad x")
+        _need(h.shape == (n_rows, d) and h.is_contiguous(), "gather_add_rmsnorm: bad output")
+        _need(rows.dtype == torch.int32 and rows.numel() >= n_rows, "gather_add_rmsnorm: rows")
+        if delta is not None:
+            _need(delta.shape == (t, d) and delta.is_contiguous(), "gather_add_rmsnorm: delta")
+        self.launches += 1
+        _check(self._add_rmsnorm(_ptr(x), _ptr(delta),
+                                 _code(delta.dtype) if delta is not None else 0,
+                                 _ptr(weight), _code(weight.dtype), float(eps), _ptr(h),
+                                 _code(h.dtype), n_rows, d, _ptr(rows), self._stream()),
+               "gather_add_rmsnorm")
+
+    def prepare_weight(self, w):
+        """A matrix [out, in] made ready for ``linear`` (contiguous, on device)."""
+        return w.contiguous()
+
+    def linear(self, a, w, out) -> None:
+        """``out[M, N] = a[M, K] @ w[N, K]^T`` with float32 accumulation."""
+        m, k = a.shape
+        n = w.shape[0]
+        _need(w.shape == (n, k) and out.shape == (m, n), "linear: shapes do not fit")
+        _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(),
+              "linear: operands must be contiguous")
+        if m == 0:
+            return
+        if w.dtype == torch.float32:
+            # a matrix held in 32 bits is multiplied in true 32-bit arithmetic
+            a32 = a if a.dtype == torch.float32 else a.float()
+            o32 = out if out.dtype == torch.float32 else torch.empty(
+                (m, n), dtype=torch.float32, device=out.device)
+            self.launches += 1
+            _check(self._gemm_f32(_ptr(a32), _ptr(w), _ptr(o32), m, n, k, self._stream()),
+                   "gemm_f32")
+            if o32 is not out:
+                out.copy_(o32)
+            return
+        _need(w.dtype == torch.bfloat16, f"linear: weight dtype {w.dtype}")
+        a16 = a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
+        self.launches += 1
+        if out.dtype == torch.float32:
+            torch.mm(a16, w.t(), out_dtype=torch.float32, out=out)
+        else:
+            torch.mm(a16, w.t(), out=out)
+
+    def rope_store(self, qkv, positions, cos, sin, slot_map, k_pool, v_pool, n_tokens: int,
+                   n_heads: int, n_kv: int, hd: int, max_pos: int, writes: bool) -> None:
+        _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv) * hd,
+              "rope_store: bad qkv")
+        _need(k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype,
+              "rope_store: cache and activations differ in type")
+        _need(k_pool.is_contiguous() and v_pool.is_contiguous(), "rope_store: pool layout")
+        pages, kvh, block, hd2 = k_pool.shape
+        _need(kvh == n_kv and hd2 == hd, "rope_store: pool shape does not fit the heads")
+        _need(cos.shape == (max_pos, hd // 2) and cos.dtype == torch.float32,
+              "rope_store: bad tables")
+        self.launches += 1
+        _check(self._rope_store(_ptr(qkv), _code(qkv.dtype), _ptr(positions), _ptr(cos),
+                                _ptr(sin), _ptr(slot_map), _ptr(k_pool), _ptr(v_pool),
+                                n_tokens, n_heads, n_kv, hd, block, max_pos,
+                                pages * block, 1 if writes else 0, _ptr(self.status),
+                                self._stream()), "rope_store")
+
+    def require_attention(self, hd: int) -> None:
+        """Make sure attention kernels for this head size exist, or say why not."""
+        _need(hd % 16 == 0 and 16 <= hd <= 256,
+              f"attention kernels take head sizes 16..256 in steps of 16, not {hd}")
+
+    def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
+                        scale: float, window: int) -> None:
+        g = step.groups[cache.group]
+        t = step.n_tokens
+        _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
+        _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
+        self.launches += 1
+        _check(self._attention_simt(
+            _ptr(qkv), _ptr(out), _code(qkv.dtype), _ptr(cache.k_pool), _ptr(cache.v_pool),
+            _ptr(g.block_table), g.max_blocks, _ptr(step.positions), _ptr(step.req_of_token),
+            t, n_heads, n_kv, hd, g.block_size, float(scale), int(window), self._stream()),
+            "attention_simt")
+
+    def swiglu(self, gu, out) -> None:
+        t, inter = out.shape
+        _need(gu.shape == (t, 2 * inter) and gu.dtype == out.dtype, "swiglu: shapes")
+        _need(gu.is_contiguous() and out.is_contiguous(), "swiglu: layout")
+        self.launches += 1
+        _check(self._swiglu(_ptr(gu), _ptr(out), _code(out.dtype), t, inter, self._stream()),
+               "swiglu")
+
+    def sample(self, logits, temperature, uniform, out) -> None:
+        """Tokens for float32 ``logits [n, V]``; rows with temperature <= 0 (or
+        ``temperature`` None) take the arg max, lowest index on ties."""
+        n, v = logits.shape
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits")
+        _need(out.dtype == torch.int32 and out.numel() >= n, "sample: out")
+        if temperature is not None:
+            _need(temperature.dtype == torch.float32 and uniform.dtype == torch.float32,
+                  "sample: temperature and uniform must be float32")
+        self.launches += 1
+        _check(self._sample(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), n, v,
+                            self._stream()), "sample")
+
+
+class Runtime:
+    """Device, element types, kernels and step buffers shared by a model's parts."""
+
+    residual_dtype = torch.float32
+    logits_dtype = torch.float32
+
+    def __init__(self, device="cuda:0", dtype: torch.dtype = torch.bfloat16):
+        self.device = torch.device(device)
+        self.act_dtype = dtype
+        self.ops = Ops(self.device, dtype)
+        self._buffers: dict = {}
+
+    def buffer(self, tag: str, shape: tuple, dtype: torch.dtype):
+        """A step buffer: the same memory for the same tag, grown when needed."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (tag, dtype)
+        flat = self._buffers.get(key)
+        if flat is None or flat.numel() < n:
+            flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._buffers[key] = flat
+        return flat[:n].view(shape)
