@@ -151,7 +151,18 @@ class CacheManager:
     def live(self) -> list:
         return list(self._records)
 
-    def can_hold(self, n_tokens: int) -> bool:
+    def _most_pages(self, g: PagedGroup, n_tokens: int, portion: int | None) -> int:
+        """Most pages of group ``g`` a request of ``n_tokens`` holds at one time
+        when it is fed at most ``portion`` tokens a step (all at once if None)."""
+        need = self.pages_for(n_tokens)
+        w = g.spec.window
+        if w is not None and portion is not None:
+            # keys older than the window are given back after every step; one
+            # page more because the live span need not start at a page's edge
+            need = min(need, self.pages_for(w - 1 + portion) + 1)
+        return need
+
+    def can_hold(self, n_tokens: int, portion: int | None = None) -> bool:
         """Could a new request with ``n_tokens`` be admitted right now?
 
         The reference's admission test, ``can_allocate(len(tokens) + 1)``
@@ -159,12 +170,15 @@ class CacheManager:
         """
         if self.slots.num_free == 0:
             return False
-        need = self.pages_for(n_tokens)
-        return all(g.pool.num_free >= need for g in self.paged)
+        return all(g.pool.num_free >= self._most_pages(g, n_tokens, portion)
+                   for g in self.paged)
 
-    def fits_at_all(self, n_tokens: int) -> bool:
+    def fits_at_all(self, n_tokens: int, portion: int | None = None) -> bool:
         """Could ``n_tokens`` ever be held, with every page free?"""
-        return self.pages_for(n_tokens) <= min(self.num_blocks, self.max_blocks)
+        if self.pages_for(n_tokens) > self.max_blocks:
+            return False
+        return all(self._most_pages(g, n_tokens, portion) <= self.num_blocks
+                   for g in self.paged)
 
     def admit(self, owner) -> bool:
         """Open an empty record for ``owner``; False if no state slot is free."""

@@ -1,0 +1,96 @@
+"""The engine: scheduler + step function + sampler behind the reference's names.
+
+Reference: ``Engine(model, num_blocks=256, block_size=16, max_batch=16, ...)``,
+``submit(prompt, max_new_tokens=32, eos_token=None) -> Request``, ``step() -> bool``,
+``run_until_done(max_steps=10_000) -> {"wall_s", "generated_tokens",
+"tokens_per_s", "requests"}`` (serve/engine.py:163-185,229-267).
+"""
+
+from __future__ import annotations
+
+import time
+
+from ..sampling.sampler import Sampler, uniform_for
+from .batch import Entry
+from .request import Request
+from .runner import ModelRunner
+from .scheduler import Scheduler
+
+
+class Engine:
+    def __init__(self, model, num_blocks: int = 256, block_size: int = 16, max_batch: int = 16,
+                 max_tokens_per_step: int = 2048, chunk_size: int = 2048):
+        self.model = model
+        self.runner = ModelRunner(model, num_blocks=num_blocks, block_size=block_size,
+                                  max_requests=max_batch)
+        self.cache = self.runner.cache
+        self.max_seq_len = model.config.max_seq_len
+        self.scheduler = Scheduler(self.cache, max_batch, max_tokens_per_step, chunk_size,
+                                   self.max_seq_len)
+        self.sampler = Sampler(model.runtime, max_rows=max_batch)
+        self._next_id = 0
+        self.step_tokens: list = []
+
+    # the reference's attribute names
+    @property
+    def waiting(self):
+        return self.scheduler.waiting
+
+    @property
+    def running(self):
+        return self.scheduler.running
+
+    @property
+    def finished(self):
+        return self.scheduler.finished
+
+    @property
+    def steps(self) -> int:
+        return self.scheduler.steps
+
+    def submit(self, prompt, max_new_tokens: int = 32, eos_token=None,
+               temperature: float = 0.0, seed: int = 0) -> Request:
+        req = Request(self._next_id, list(prompt), int(max_new_tokens), eos_token,
+                      float(temperature), int(seed))
+        self.scheduler.add(req)
+        self._next_id += 1
+        return req
+
+    def step(self) -> bool:
+        """One scheduler iteration; True while work remains (serve/engine.py:229-256)."""
+        if not self.scheduler.has_work():
+            return False
+        plan = self.scheduler.plan()
+        entries = []
+        for p in plan.entries:
+            r = p.request
+            toks = r.tokens[r.num_computed:r.num_computed + p.n_tokens]
+            entries.append(Entry(r.req_id, toks, [p.n_tokens - 1] if p.wants_logits else []))
+        logits = self.runner.step(entries)
+        sampled = {}
+        if logits is not None:
+            wanting = [p.request for p in plan.entries if p.wants_logits]
+            temps = [r.temperature for r in wanting]
+            us = [uniform_for(r.seed, r.req_id, len(r.generated)) if r.temperature > 0 else 0.0
+                  for r in wanting]
+            toks = self.sampler.sample(logits, temps, us)
+            sampled = {r.req_id: t for r, t in zip(wanting, toks)}
+        self.scheduler.complete(plan, sampled)
+        self.step_tokens.append(plan.n_tokens)
+        return self.scheduler.has_work()
+
+    def run_until_done(self, max_steps: int = 10_000) -> dict:
+        t0 = time.perf_counter()
+        start = self.scheduler.steps
+        while self.step():
+            if self.scheduler.steps - start >= max_steps:
+                raise RuntimeError("engine exceeded max_steps")
+        self.model.runtime.ops.check_status()
+        wall = time.perf_counter() - t0
+        toks = sum(len(r.generated) for r in self.finished)
+        return {"wall_s": wall, "generated_tokens": toks,
+                "tokens_per_s": toks / wall if wall > 0 else float("inf"),
+                "requests": len(self.finished), "steps": self.scheduler.steps,
+                "preemptions": self.scheduler.preemptions,
+                "page_high_water": max((g.pool.high_water for g in self.cache.paged),
+                                       default=0)}

@@ -1,0 +1,44 @@
+"""The Python entry point: load or draw a model, generate from token prompts.
+
+The reference's entry is ``Engine(model, ...)`` + ``submit`` + ``run_until_done``
+with the result in ``req.generated`` (serve/engine.py:163-185,258-267;
+serve/api.py:92-97).  ``LLM`` wraps the same three calls.
+"""
+
+from __future__ import annotations
+
+from ..config.registry import config_from_dict
+from .engine import Engine
+from .runner import load_model, random_model
+
+
+class LLM:
+    def __init__(self, model, **engine_options):
+        self.model = model
+        self.config = model.config
+        self.engine = Engine(model, **engine_options)
+
+    @classmethod
+    def from_folder(cls, folder, dtype: str | None = None, device="cuda:0",
+                    **engine_options) -> "LLM":
+        return cls(load_model(folder, dtype=dtype, device=device), **engine_options)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, norm_std: float = 0.0,
+                    dtype: str | None = None, device="cuda:0", fast: bool = False,
+                    **engine_options) -> "LLM":
+        if isinstance(config, dict):
+            config = config_from_dict(config)
+        return cls(random_model(config, seed, norm_std, dtype, device, fast), **engine_options)
+
+    def generate(self, prompts, max_new_tokens: int = 32, temperature: float = 0.0,
+                 seed: int = 0, eos=None) -> list:
+        """New tokens for each prompt (lists of token ids in, lists out).
+
+        All prompts are submitted at once and served by continuous batching.
+        Request i draws with the key (seed, i-th id of this engine), so the
+        result does not depend on how the requests were batched.
+        """
+        reqs = [self.engine.submit(p, max_new_tokens, eos, temperature, seed) for p in prompts]
+        self.engine.run_until_done(max_steps=10_000_000)
+        return [list(r.generated) for r in reqs]

@@ -1,0 +1,108 @@
+"""Generation through the entry points on the GPU, against the plain implementation."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_llama as P
+from engine_helpers import RND, make_folder, tokens_for
+from mini_llm_stack_b200.engine.llm import LLM
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("gen_models")
+    return {(k, d): make_folder(tmp, k, d) for k in "ABC" for d in ("float32", "bfloat16")}
+
+
+def test_greedy_generation_matches_plain_token_for_token(folders):
+    # tiny-A: 3 prompts of 5/17/33 tokens, 16 new tokens each, float32
+    folder, cfg, w = folders[("A", "float32")]
+    prompts = [tokens_for(256, n, 20 + n) for n in (5, 17, 33)]
+    llm = LLM.from_folder(folder, dtype="float32", num_blocks=32, max_batch=4)
+    got = llm.generate(prompts, max_new_tokens=16)
+    for p, g in zip(prompts, got):
+        assert g == P.plain_generate(w, cfg, p, 16)
+
+
+def test_temperature_sampling_with_chunks_and_small_pages(folders):
+    # tiny-B: 4 prompts of 1/9/40/77, portions of 16, pages of 8, temperature 0.8
+    folder, cfg, w = folders[("B", "float32")]
+    prompts = [tokens_for(97, n, 30 + n) for n in (1, 9, 40, 77)]
+    llm = LLM.from_folder(folder, dtype="float32", num_blocks=64, block_size=8, max_batch=4,
+                          chunk_size=16, max_tokens_per_step=40)
+    got = llm.generate(prompts, max_new_tokens=12, temperature=0.8, seed=5)
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        assert g == P.plain_generate(w, cfg, p, 12, temperature=0.8, seed=5, request=i)
+    assert max(llm.engine.step_tokens) <= 40
+    # the same requests alone, one at a time, draw the same tokens
+    for i, p in enumerate(prompts):
+        solo = LLM.from_folder(folder, dtype="float32", num_blocks=64, block_size=8)
+        solo.engine._next_id = i
+        assert solo.generate([p], max_new_tokens=12, temperature=0.8, seed=5)[0] == got[i]
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.7])
+def test_running_out_of_pages_does_not_change_the_output(folders, temperature):
+    folder, cfg, w = folders[("C", "float32")]
+    prompts = [tokens_for(301, n, 50 + n) for n in (20, 31, 7, 44, 12, 26)]
+    roomy = LLM.from_folder(folder, dtype="float32", num_blocks=64, max_batch=6)
+    want = roomy.generate(prompts, max_new_tokens=24, temperature=temperature, seed=3)
+    assert roomy.engine.scheduler.preemptions == 0
+    tight = LLM.from_folder(folder, dtype="float32", num_blocks=12, max_batch=6, chunk_size=24)
+    got = tight.generate(prompts, max_new_tokens=24, temperature=temperature, seed=3)
+    assert tight.engine.scheduler.preemptions > 0
+    assert got == want
+    assert tight.engine.cache.num_free_pages() == 12
+    tight.engine.cache.check()
+    if temperature == 0.0:
+        assert got[2] == P.plain_generate(w, cfg, prompts[2], 24)
+
+
+def test_bfloat16_greedy_tokens_are_maxima_of_the_plain_logits(folders):
+    folder, cfg, w = folders[("B", "bfloat16")]
+    prompts = [tokens_for(97, n, 70 + n) for n in (3, 50)]
+    llm = LLM.from_folder(folder, dtype="bfloat16", num_blocks=32)
+    got = llm.generate(prompts, max_new_tokens=10)
+    for p, g in zip(prompts, got):
+        logits = P.plain_forward(w, cfg, p + g, RND["bfloat16"])
+        for i, tok in enumerate(g):
+            row = logits[len(p) - 1 + i]
+            assert row[tok] >= row.max() - 1e-2 * row.abs().max()
+
+
+def test_eos_and_long_decoding(folders):
+    folder, cfg, w = folders[("A", "float32")]
+    p = tokens_for(256, 11, 99)
+    ref = P.plain_generate(w, cfg, p, 200)
+    llm = LLM.from_folder(folder, dtype="float32", num_blocks=32)
+    assert llm.generate([p], max_new_tokens=200)[0] == ref        # 200 decoded tokens
+    eos = ref[7]
+    cut = ref[:ref.index(eos) + 1]
+    assert llm.generate([p], max_new_tokens=200, eos=eos)[0] == cut
+
+
+def test_command_line_chat(folders, tmp_path):
+    folder, cfg, w = folders[("A", "float32")]
+    p = tokens_for(256, 9, 4)
+    want = P.plain_generate(w, cfg, p, 8)
+    proc = subprocess.run(
+        [sys.executable, "-m", "mini_llm_stack_b200.api", "chat", "--model", str(folder),
+         "--dtype", "float32", "--token-ids", ",".join(map(str, p)), "--max-new", "8"],
+        capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.strip().endswith(f"-> {','.join(map(str, want))!r}")
+    # text goes in and out as bytes when the vocabulary has 256 entries
+    proc = subprocess.run(
+        [sys.executable, "-m", "mini_llm_stack_b200.api", "chat", "--model", str(folder),
+         "--dtype", "float32", "-p", "kernel ", "--max-new", "5"],
+        capture_output=True, text=True, cwd=ROOT, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.startswith("'kernel ' -> ")

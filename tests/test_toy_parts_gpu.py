@@ -1,0 +1,150 @@
+"""Another mixer, with state of its own, registered and run from a test.
+
+The mixer, its architecture and its configuration are defined here; no file of
+the framework knows them.  The mixer keeps a fixed-size state per request (a
+decaying sum of its inputs), so it needs a state slot instead of pages; the toy
+model alternates it with the framework's attention, so one model holds a paged
+group and a fixed-state group.
+"""
+
+from dataclasses import asdict, dataclass
+
+import pytest
+import torch
+
+import plain_llama as P
+from engine_helpers import Replayer, assert_close, tokens_for
+from mini_llm_stack_b200.config import (config_from_folder, register_architecture,
+                                        unregister_architecture)
+from mini_llm_stack_b200.parts import (ComposedModel, FixedState, GroupedQueryAttention,
+                                       LayerCall, Mixer, OutputHead, PreNormBlock, RMSNorm,
+                                       RotaryPosition, SwiGLUFeedForward, TensorSpec,
+                                       TokenEmbedding)
+from mini_llm_stack_b200.weights import write_random_model
+from safetensors.torch import load_file
+
+pytestmark = pytest.mark.gpu
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    architecture: str = "toy_decay"
+    vocab_size: int = 53
+    d_model: int = 48
+    n_layers: int = 3
+    n_heads: int = 3
+    head_dim: int = 16
+    intermediate_size: int = 72
+    max_seq_len: int = 128
+    decay: float = 0.75
+    norm_eps: float = 1e-5
+    rope_theta: float = 1000.0
+    dtype: str = "float32"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**raw)
+
+    def to_dict(self):
+        return asdict(self)
+
+
+class DecayMixer(Mixer):
+    """``s_t = decay * s_{t-1} + h_t``; ``out_t = W s_t``.  State: s, per request."""
+
+    def __init__(self, d_model, decay):
+        self.d, self.decay = d_model, decay
+
+    def tensor_specs(self):
+        return {"w.weight": TensorSpec((self.d, self.d))}
+
+    def cache_spec(self):
+        return FixedState((self.d,), torch.float32)
+
+    def bind(self, tensors, runtime):
+        self.runtime = runtime
+        self.w = tensors["w.weight"].float()
+
+    def forward(self, h, step, cache):
+        out = torch.empty_like(h)
+        slots = step.state_slot.tolist()
+        at = 0
+        for r, n in enumerate(step.q_lens):
+            s = cache.state[slots[r]]
+            for i in range(n):
+                s = self.decay * s + h[at + i].float()
+                out[at + i] = (s @ self.w.t()).to(h.dtype)
+            cache.state[slots[r]] = s
+            at += n
+        return out
+
+
+def build_toy(cfg):
+    emb = TokenEmbedding(cfg.vocab_size, cfg.d_model)
+    blocks = []
+    for i in range(cfg.n_layers):
+        if i % 2 == 0:
+            mixer = DecayMixer(cfg.d_model, cfg.decay)
+        else:
+            mixer = GroupedQueryAttention(
+                cfg.d_model, cfg.n_heads, cfg.n_heads, cfg.head_dim, cfg.head_dim ** -0.5,
+                RotaryPosition(cfg.head_dim, cfg.rope_theta, cfg.max_seq_len))
+        blocks.append(PreNormBlock(RMSNorm(cfg.d_model, cfg.norm_eps), mixer,
+                                   RMSNorm(cfg.d_model, cfg.norm_eps),
+                                   SwiGLUFeedForward(cfg.d_model, cfg.intermediate_size),
+                                   names=("norm_a", "mix", "norm_b", "ffn")))
+    calls = [LayerCall(i, i, True) for i in range(cfg.n_layers)]
+    return ComposedModel(cfg, emb, blocks, calls, RMSNorm(cfg.d_model, cfg.norm_eps),
+                         OutputHead(cfg.vocab_size, cfg.d_model, tied_to=emb))
+
+
+def plain_toy(w, cfg, tokens):
+    """The toy model on whole sequences with the plain parts."""
+    toks = torch.as_tensor(tokens)
+    S = len(tokens)
+    x = w["embed.weight"][toks]
+    cos, sin = P.plain_rotary_tables(cfg.head_dim, cfg.max_seq_len, cfg.rope_theta)
+    attn_cfg = dict(n_heads=cfg.n_heads, n_kv_heads=cfg.n_heads, head_dim=cfg.head_dim)
+    for i in range(cfg.n_layers):
+        p = f"blocks.{i}"
+        h = P.plain_rmsnorm(x, w[f"{p}.norm_a.weight"], cfg.norm_eps)
+        if i % 2 == 0:
+            s = torch.zeros(cfg.d_model)
+            rows = []
+            for t in range(S):
+                s = cfg.decay * s + h[t]
+                rows.append(s @ w[f"{p}.mix.w.weight"].t())
+            a = torch.stack(rows)
+        else:
+            a, _ = P.plain_mixer(h, w, f"{p}.mix", attn_cfg, cos, sin, torch.arange(S), None)
+        x = x + a
+        h = P.plain_rmsnorm(x, w[f"{p}.norm_b.weight"], cfg.norm_eps)
+        x = x + P.plain_swiglu(h, w[f"{p}.ffn.w_gate.weight"], w[f"{p}.ffn.w_up.weight"],
+                               w[f"{p}.ffn.w_down.weight"])
+    return P.plain_rmsnorm(x, w["final_norm.weight"], cfg.norm_eps) @ w["embed.weight"].t()
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    register_architecture("toy_decay", ToyConfig, build_toy)
+    try:
+        cfg = ToyConfig()
+        write_random_model(tmp_path / "toy", cfg, seed=2, norm_std=0.1)
+        assert config_from_folder(tmp_path / "toy") == cfg
+        w = {n: t.float() for n, t in
+             load_file(str(tmp_path / "toy" / "model.safetensors")).items()}
+        rp = Replayer(tmp_path / "toy", "float32", num_blocks=12, max_requests=3)
+        cache = rp.runner.cache
+        assert len(cache.paged) == 1 and len(cache.fixed) == 1
+        assert cache.fixed[0].members == [0, 2] and cache.paged[0].members == [1]
+        toks = {i: tokens_for(cfg.vocab_size, n, 60 + i) for i, n in enumerate([37, 21, 50, 9])}
+        # portions and single tokens of three live requests; the fourth request
+        # takes over the state slot and the pages of a finished one
+        rp.step([(0, 20), (1, 2)], toks)
+        rp.step([(0, 1), (1, 19), (2, 30)], toks, end=[1])
+        rp.step([(0, 16), (2, 1), (3, 9)], toks, end=[0, 3])
+        rp.step([(2, 19)], toks, end=[2])
+        for i in toks:
+            assert_close(rp.logits(i), plain_toy(w, cfg, toks[i]), "float32", f"toy request {i}")
+        assert cache.slots.num_free == 3
+    finally:
+        unregister_architecture("toy_decay")
