@@ -1,0 +1,295 @@
+"""Decode and prefill throughput of the engine at the Llama-3-8B shape.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W]
+
+One JSON line: ``value`` = decoded tokens a second at batch 8 with every request
+near the context length (a step = one decode step of the whole batch), timed on
+the device around the step function; ``e2e`` = the same through the Python entry
+point (``Engine.step``: host token lists in, sampled tokens out); ``prefill`` =
+one 2,048-token prompt in one step; ``roofline`` = bytes the decode step has to
+read (every weight once + the live requests' cache) over its time, against the
+measured copy bandwidth; ``points`` = decode at batch 1 and 64.
+
+Weights are random (N(0, 0.02), drawn on the device), token ids uniform; the
+caches of the decode runs are filled with random keys and values instead of
+being computed, which changes no byte count and no kernel.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+
+# BASELINE.json configs[2]: Llama-3-8B shape
+MODEL = dict(architecture="llama_dense", vocab_size=128256, d_model=4096, n_layers=32,
+             n_heads=32, n_kv_heads=8, head_dim=128, intermediate_size=14336,
+             max_seq_len=8192, rope_theta=500000.0, norm_eps=1e-5, tie_embeddings=False,
+             dtype="bfloat16")
+FULL_LAYERS = 32
+PAGE = 16
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            raw = json.loads(p.read_text())
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if k in raw and raw[k]:
+                    out[k] = float(raw[k])
+            return out, "measured"
+        except (ValueError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self) -> int:
+        return len(self.rows)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, lo: int = 0, hi: int | None = None) -> dict:
+        rows = [r for r in self.rows[lo:hi] if len(r) >= 6 and r[0].isdigit()]
+        if not rows:
+            rows = [r for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower() == "active" for r in rows)]
+        return {"sm_mhz": statistics.median(int(r[0]) for r in rows),
+                "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def weight_bytes(cfg, layers: int) -> int:
+    d, hd = cfg["d_model"], cfg["head_dim"]
+    per_layer = ((cfg["n_heads"] + 2 * cfg["n_kv_heads"]) * hd * d + d * cfg["n_heads"] * hd
+                 + 3 * cfg["intermediate_size"] * d + 2 * d)
+    return 2 * (per_layer * layers + cfg["vocab_size"] * d + d)
+
+
+def kv_bytes_per_token(cfg, layers: int) -> int:
+    return 2 * 2 * cfg["n_kv_heads"] * cfg["head_dim"] * layers
+
+
+def prefill_flops(cfg, layers: int, t: int) -> float:
+    d, hd = cfg["d_model"], cfg["head_dim"]
+    lin = ((cfg["n_heads"] + 2 * cfg["n_kv_heads"]) * hd * d + d * cfg["n_heads"] * hd
+           + 3 * cfg["intermediate_size"] * d)
+    attn = 2 * 2 * cfg["n_heads"] * hd * (t * (t + 1) / 2)       # QK^T and PV, causal
+    return layers * (2.0 * lin * t + attn) + 2.0 * cfg["vocab_size"] * d
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=48)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=MODEL["max_seq_len"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "grenver/mini-llm-stack has no setup.py or pyproject.toml, so the "
+                          "offline pip install into baseline/_ref fails: not installable"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    from mini_llm_stack_b200.config import config_from_dict
+    from mini_llm_stack_b200.engine.batch import Entry
+    from mini_llm_stack_b200.engine.engine import Engine
+    from mini_llm_stack_b200.engine.runner import random_model
+
+    pk, pk_src = peaks()
+    raw = dict(MODEL, n_layers=args.layers)
+    cfg = config_from_dict(raw)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    model = random_model(cfg, seed=0, device=dev, fast=True)
+    ops = model.runtime.ops
+    ctx = min(args.context, cfg.max_seq_len)
+    max_b = max(args.batch, 1 if args.no_points else 64)
+    pages_per_req = (ctx + PAGE - 1) // PAGE
+    engine = Engine(model, num_blocks=max_b * pages_per_req + 8, block_size=PAGE,
+                    max_batch=max_b, max_tokens_per_step=max(PREFILL_TOKENS, max_b),
+                    chunk_size=PREFILL_TOKENS)
+    runner, cache = engine.runner, engine.cache
+    for g in cache.paged:                       # keys and values as a prefill would leave them
+        for m in range(g.kv.shape[0]):
+            g.kv[m].normal_(0.0, 1.0)
+    gen = torch.Generator().manual_seed(1)
+
+    def rand_tokens(n):
+        return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+
+    clocks = ClockSampler()
+    clocks.start()
+
+    def timed(fn, n_warm, n_timed):
+        for _ in range(n_warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = ops.launches
+        e0.record()
+        for _ in range(n_timed):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n_timed, (ops.launches - l0)
+
+    # ------------------------------------------------------------------ prefill
+    def prefill_once():
+        toks = rand_tokens(PREFILL_TOKENS)
+        e = [Entry("prefill", toks, [PREFILL_TOKENS - 1])]
+        runner.reserve(e)
+        runner.step(e)
+        runner.release("prefill")
+
+    prefill_ms, _ = timed(prefill_once, 3, 5)
+    pf = prefill_flops(raw, args.layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 3),
+               "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ------------------------------------------------------------------- decode
+    def decode_run(batch, n_warm, n_timed):
+        """Device time of one decode step with ``batch`` requests that end at ``ctx``."""
+        start = ctx - (n_warm + n_timed)
+        ids = [f"d{batch}_{i}" for i in range(batch)]
+        for r in ids:
+            cache.admit(r)
+            assert cache.reserve(r, start)
+            cache.commit(r, start)              # the cache holds random keys and values
+        last = [rand_tokens(1)[0] for _ in ids]
+        out = torch.empty(batch, dtype=torch.int32, device=dev)
+
+        def one():
+            e = [Entry(r, [t], [0]) for r, t in zip(ids, last)]
+            runner.reserve(e)
+            logits = runner.step(e)
+            ops.sample(logits, None, None, out)
+
+        ms, launches = timed(one, n_warm, n_timed)
+        mean_ctx = start + n_warm + (n_timed + 1) / 2
+        for r in ids:
+            runner.release(r)
+        return ms, launches, mean_ctx
+
+    mark0 = clocks.mark()
+    ms, launches, mean_ctx = decode_run(args.batch, warmup, steps)
+    mark1 = clocks.mark()
+    value = args.batch / ms * 1e3
+    step_bytes = weight_bytes(raw, args.layers) + args.batch * mean_ctx * kv_bytes_per_token(
+        raw, args.layers)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _ = decode_run(b, 3, max(8, steps // 4))
+            points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+
+    # ---------------------------------------------------- end to end (Engine API)
+    prompt_len = ctx - (warmup + steps) - 1
+    reqs = [engine.submit(rand_tokens(prompt_len), max_new_tokens=warmup + steps + 1)
+            for _ in range(args.batch)]
+    while any(r.remaining > 1 or not r.generated for r in reqs):
+        engine.step()                            # prompts in portions, untimed
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n0 = sum(len(r.generated) for r in reqs)
+    for _ in range(steps - 1):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    e2e_tokens = sum(len(r.generated) for r in reqs) - n0
+    h2d = runner.builder.last_bytes
+    engine.run_until_done()
+    clocks.stop()
+
+    line = {
+        "metric": "decode tok/s at batch 8, Llama-3-8B shape, context 8192 "
+                  "(batch 1/64 in points; prefill tok/s at 2,048 tokens in prefill)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "llama-3-8b-shape", "layers": args.layers,
+                   "layers_of_config": FULL_LAYERS, "hidden": raw["d_model"],
+                   "heads": raw["n_heads"], "kv_heads": raw["n_kv_heads"],
+                   "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
+                   "vocab": raw["vocab_size"], "global_batch": args.batch, "seq_len": ctx,
+                   "page_size": PAGE, "weights": "random N(0,0.02)", "parallelism": "none",
+                   "l2": "inputs larger than L2 (weights and cache are read once a step)",
+                   "peaks": pk_src},
+        "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": int(launches),
+        "library_gemm_launches": int(getattr(ops, "library_launches", 0)),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(mark0, mark1),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

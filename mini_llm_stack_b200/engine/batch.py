@@ -47,6 +47,7 @@ class BatchBuilder:
         self._events = [None, None]
         self._turn = 0
         self._dev = None
+        self.last_bytes = 0           # bytes of the last step's host-to-device copy
 
     def _staging(self, n: int):
         use_cuda = self.device.type == "cuda"
@@ -140,6 +141,7 @@ class BatchBuilder:
             view(f"table{gid}")[:] = table.reshape(-1)
 
         dev = self._dev
+        self.last_bytes = cur * 4
         if self.device.type == "cuda":
             dev[:cur].copy_(pinned[:cur], non_blocking=True)
             ev = self._events[which] or torch.cuda.Event()

@@ -89,7 +89,8 @@ class Ops:
         self._gemm = None
         self.attention_impl = os.environ.get("MLS_B200_ATTENTION", "auto")
         self.gemm_impl = os.environ.get("MLS_B200_GEMM", "auto")
-        self.launches = 0
+        self.launches = 0            # launches of this package's own kernels
+        self.library_launches = 0    # plain matrix products handed to the library
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -168,7 +169,7 @@ class Ops:
             return
         _need(w.dtype == torch.bfloat16, f"linear: weight dtype {w.dtype}")
         a16 = a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
-        self.launches += 1
+        self.library_launches += 1
         if out.dtype == torch.float32:
             torch.mm(a16, w.t(), out_dtype=torch.float32, out=out)
         else:

@@ -43,6 +43,16 @@ MODULES = {
 }
 
 
+def all_modules(head_sizes=()) -> list:
+    """Every (module, defines) pair there is to build, for the given head sizes."""
+    out = [("core", {})]
+    if (CSRC / "attention_mma.cu").is_file():
+        out += [("attention", {"MLS_HEAD_DIM": int(h)}) for h in head_sizes]
+    if (CSRC / "gemm_tcgen05.cu").is_file():
+        out.append(("gemm", {}))
+    return out
+
+
 class KernelBuildError(RuntimeError):
     pass
 
