@@ -1,0 +1,576 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16),
+// compiled for one head size (MLS_HEAD_DIM, a multiple of 16).
+//
+// Reference math (train/model.py:55-70): S = (q . k) * scale, key j hidden from
+// the query at absolute position p iff j > p (or j <= p - window); softmax and
+// P . V with float32 scores, maxima, sums and accumulators; P is rounded to
+// bfloat16 for the second product, as in the reference's prefill kernel
+// (kernels/attention_fwd.py:106).  Pages are walked through the block table as
+// in its decode kernel (kernels/paged_attention.py:60-66).
+//
+// Rows of a tile are (token, head-in-group) pairs of ONE kv head, so the keys and
+// values of a kv head are loaded once for all G query heads that share it.
+//
+//  attention_tile_kernel   64 rows per CTA, 16 per warp: prompts and portions.
+//  attention_split_kernel  up to 16 rows per CTA (single decoded tokens, portions
+//                          of a few tokens), the keys of a tile split over the 4
+//                          warps, the context split over gridDim.z CTAs; partial
+//                          results go to scratch memory and are merged by
+//  attention_merge_kernel.
+#include "common.cuh"
+
+#ifndef MLS_HEAD_DIM
+#error "compile with -DMLS_HEAD_DIM=<head size>"
+#endif
+
+namespace {
+constexpr int HD = MLS_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head sizes 16..256 in steps of 16");
+constexpr int BN = 64;                   // keys per tile
+constexpr int NT = 128;                  // threads per CTA
+constexpr int ROWB = HD * 2 + 16;        // bytes of a padded row in shared memory: the
+                                         // 16 extra bytes spread 8 rows over all banks
+constexpr int KCH = HD / 8;              // 16-byte chunks per row
+constexpr int TILE_BYTES = BN * ROWB;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct Params {
+    const __nv_bfloat16* qkv;            // [T, (H + 2 Hkv) * HD]
+    __nv_bfloat16* out;                  // [T, H * HD]
+    const __nv_bfloat16* k_pool;         // [pages, Hkv, block, HD]
+    const __nv_bfloat16* v_pool;
+    const int* block_table;              // [R, max_blocks], -1 = no page
+    const int* cu_q;                     // [R + 1]
+    const int* ctx_len;                  // [R]
+    float* part_o;                       // [splits, T * H, HD]   (split kernel, splits > 1)
+    float* part_lse;                     // [splits, T * H]       (log2 domain)
+    int max_blocks, n_req, n_tokens, n_heads, n_kv, group, block_size, window, n_split;
+    int small_only;                      // tile kernel: 1 = skip requests the split kernel takes
+    float scale_log2;                    // scale * log2(e)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;       // size 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x by the special function unit (relative error about 2^-22; 2^-inf = 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A request goes to the split kernel when all its (token, head) rows of one kv
+// head fit one 16-row tile.
+__device__ __forceinline__ bool is_small(int q_len, int group) { return q_len * group <= 16; }
+
+// Keys kbase .. kbase+63 of one kv head into shared memory; rows outside [lo, hi]
+// or on a released page are zero-filled, so nothing that is not a key of this
+// request can reach the products.
+__device__ __forceinline__ void load_kv_tile(uint8_t* ks, uint8_t* vs, const Params& P,
+                                             const int* table, int kvh, int kbase, int lo, int hi) {
+    const uint32_t ka = smem_u32(ks), va = smem_u32(vs);
+    for (int idx = threadIdx.x; idx < BN * KCH; idx += NT) {
+        const int row = idx / KCH, ch = idx - row * KCH;
+        const int j = kbase + row;
+        bool ok = j >= lo && j <= hi;
+        size_t off = 0;
+        if (ok) {
+            const int page = table[j / P.block_size];
+            ok = page >= 0;
+            if (ok)
+                off = (((size_t)page * P.n_kv + kvh) * P.block_size + (j % P.block_size)) * HD +
+                      ch * 8;
+        }
+        cp_async16(ka + row * ROWB + ch * 16, P.k_pool + off, ok);
+        cp_async16(va + row * ROWB + ch * 16, P.v_pool + off, ok);
+    }
+}
+
+// Rows row0 .. row0+n_rows-1 of the request's (token, head) rows into shared memory.
+__device__ __forceinline__ void load_q_rows(uint8_t* qs, const Params& P, int tok0, int kvh,
+                                            int row0, int n_rows, int rows_total) {
+    const uint32_t qa = smem_u32(qs);
+    const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
+    for (int idx = threadIdx.x; idx < n_rows * KCH; idx += NT) {
+        const int rr = idx / KCH, ch = idx - rr * KCH;
+        const int row = row0 + rr;
+        const bool ok = row < rows_total;
+        size_t off = 0;
+        if (ok) {
+            const int i = row / P.group, g = row - i * P.group;
+            off = (size_t)(tok0 + i) * row_w + (size_t)(kvh * P.group + g) * HD + ch * 8;
+        }
+        cp_async16(qa + rr * ROWB + ch * 16, P.qkv + off, ok);
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// 64 rows per CTA, 16 per warp
+// ----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* qs = smem;                               // [64][ROWB]
+    uint8_t* kbuf = smem + TILE_BYTES;                // 2 x [64][ROWB]
+    uint8_t* vbuf = smem + 3 * TILE_BYTES;            // 2 x [64][ROWB]
+
+    // which request and which 64-row tile of it
+    int r = 0, tile = blockIdx.x, q_len = 0, rows = 0;
+    for (; r < P.n_req; ++r) {
+        q_len = P.cu_q[r + 1] - P.cu_q[r];
+        rows = q_len * P.group;
+        int tiles = (P.small_only && is_small(q_len, P.group)) ? 0 : (rows + 63) / 64;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (r >= P.n_req) return;
+    const int kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
+    const int row0 = tile * 64;
+    const int pos0 = ctx - q_len;                     // position of the portion's first token
+    const int i_first = row0 / P.group;
+    const int i_last = (min(rows, row0 + 64) - 1) / P.group;
+    const int hi = pos0 + i_last;
+    const int lo = P.window > 0 ? max(0, pos0 + i_first - P.window + 1) : 0;
+    const int* table = P.block_table + (size_t)r * P.max_blocks;
+    const int kbase0 = (lo / BN) * BN;
+    const int n_tiles = (hi - kbase0) / BN + 1;
+
+    load_q_rows(qs, P, tok0, kvh, row0, 64, rows);
+    load_kv_tile(kbuf, vbuf, P, table, kvh, kbase0, lo, hi);
+    cp_async_commit();
+
+    // positions of this thread's two rows (-1: the row does not exist)
+    const int rA = row0 + warp * 16 + (lane >> 2), rB = rA + 8;
+    const int pA = rA < rows ? pos0 + rA / P.group : -1;
+    const int pB = rB < rows ? pos0 + rB / P.group : -1;
+    const int loA = P.window > 0 ? pA - P.window + 1 : 0;
+    const int loB = P.window > 0 ? pB - P.window + 1 : 0;
+
+    uint32_t qf[HD / 16][4];
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+
+    for (int t = 0; t < n_tiles; ++t) {
+        cp_async_wait<0>();
+        __syncthreads();
+        if (t == 0) {
+            const uint32_t qa = smem_u32(qs) + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB +
+                                (lane >> 4) * 16;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) ldsm_x4(qf[ks], qa + ks * 32);
+        }
+        const int kbase = kbase0 + t * BN;
+        if (t + 1 < n_tiles) {
+            load_kv_tile(kbuf + ((t + 1) & 1) * TILE_BYTES, vbuf + ((t + 1) & 1) * TILE_BYTES, P,
+                         table, kvh, kbase + BN, lo, hi);
+            cp_async_commit();
+        }
+        const uint32_t ka = smem_u32(kbuf + (t & 1) * TILE_BYTES);
+        const uint32_t va = smem_u32(vbuf + (t & 1) * TILE_BYTES);
+
+        // S = Q K^T for 16 rows x 64 keys
+        float s[BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        const uint32_t kaddr = ka + ((lane & 7) + (lane >> 4) * 8) * ROWB + ((lane >> 3) & 1) * 16;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < BN / 16; ++np) {
+                uint32_t b[4];
+                ldsm_x4(b, kaddr + np * 16 * ROWB + ks * 32);
+                mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+                mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        // scale, mask, running maximum
+        float tmA = -INFINITY, tmB = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+            const int j = kbase + n * 8 + (lane & 3) * 2;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int jj = j + e;
+                const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
+                const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                s[n][e] = a;
+                s[n][2 + e] = b;
+                tmA = fmaxf(tmA, a);
+                tmB = fmaxf(tmB, b);
+            }
+        }
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1));
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
+        const float nmA = fmaxf(mA, tmA), nmB = fmaxf(mB, tmB);
+        const float baseA = nmA == -INFINITY ? 0.f : nmA, baseB = nmB == -INFINITY ? 0.f : nmB;
+        const float cA = fast_exp2(mA - baseA), cB = fast_exp2(mB - baseB);   // exp2(-inf) = 0
+        mA = nmA;
+        mB = nmB;
+        float sumA = 0.f, sumB = 0.f;
+        uint32_t pf[BN / 16][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+            const float p0 = fast_exp2(s[n][0] - baseA), p1 = fast_exp2(s[n][1] - baseA);
+            const float p2 = fast_exp2(s[n][2] - baseB), p3 = fast_exp2(s[n][3] - baseB);
+            sumA += p0 + p1;
+            sumB += p2 + p3;
+            pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        lA = lA * cA + sumA;
+        lB = lB * cB + sumB;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= cA;
+            o[i][1] *= cA;
+            o[i][2] *= cB;
+            o[i][3] *= cB;
+        }
+        // O += P V
+        const uint32_t vaddr = va + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t b[4];
+                ldsm_x4_trans(b, vaddr + kk * 16 * ROWB + dp * 32);
+                mma_bf16(o[2 * dp], pf[kk], b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pf[kk], b[2], b[3]);
+            }
+        }
+    }
+    // the row sums live in four threads each
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = half ? rB : rA;
+        if (row >= rows) continue;
+        const int i = row / P.group, g = row - i * P.group;
+        __nv_bfloat16* dst = P.out + (size_t)(tok0 + i) * P.n_heads * HD +
+                             (size_t)(kvh * P.group + g) * HD + (lane & 3) * 2;
+        const float inv = half ? invB : invA;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            *reinterpret_cast<uint32_t*>(dst + n * 8) =
+                pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// up to 16 rows per CTA, the keys of a tile split over the warps, the context over CTAs
+// ----------------------------------------------------------------------------------------
+constexpr int STAGES = 3;
+
+__global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* qs = smem;                               // [16][ROWB]
+    uint8_t* kbuf = smem + 16 * ROWB;                 // STAGES x [64][ROWB]
+    uint8_t* vbuf = kbuf + STAGES * TILE_BYTES;
+
+    const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int q_len = P.cu_q[r + 1] - P.cu_q[r];
+    if (!is_small(q_len, P.group)) return;            // the tile kernel's
+    const int rows = q_len * P.group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
+    const int pos0 = ctx - q_len;
+    const int hi = ctx - 1;
+    const int lo = P.window > 0 ? max(0, pos0 - P.window + 1) : 0;
+    const int* table = P.block_table + (size_t)r * P.max_blocks;
+    const int kbase0 = (lo / BN) * BN;
+    const int tiles_all = (hi - kbase0) / BN + 1;
+    const int per = (tiles_all + P.n_split - 1) / P.n_split;
+    const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
+    const int n_tiles = max(0, t_end - t_begin);
+
+    const int rA = lane >> 2, rB = rA + 8;
+    const int pA = rA < rows ? pos0 + rA / P.group : -1;
+    const int pB = rB < rows ? pos0 + rB / P.group : -1;
+    const int loA = P.window > 0 ? pA - P.window + 1 : 0;
+    const int loB = P.window > 0 ? pB - P.window + 1 : 0;
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+    uint32_t qf[HD / 16][4];
+
+    if (n_tiles > 0) {
+        load_q_rows(qs, P, tok0, kvh, 0, 16, rows);
+#pragma unroll
+        for (int st = 0; st < STAGES - 1; ++st) {
+            if (st < n_tiles)
+                load_kv_tile(kbuf + st * TILE_BYTES, vbuf + st * TILE_BYTES, P, table, kvh,
+                             kbase0 + (t_begin + st) * BN, lo, hi);
+            cp_async_commit();
+        }
+    }
+    for (int t = 0; t < n_tiles; ++t) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        if (t == 0) {
+            const uint32_t qa = smem_u32(qs) + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB +
+                                (lane >> 4) * 16;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) ldsm_x4(qf[ks], qa + ks * 32);
+        }
+        {
+            const int nt = t + STAGES - 1;
+            if (nt < n_tiles)
+                load_kv_tile(kbuf + (nt % STAGES) * TILE_BYTES, vbuf + (nt % STAGES) * TILE_BYTES,
+                             P, table, kvh, kbase0 + (t_begin + nt) * BN, lo, hi);
+            cp_async_commit();
+        }
+        const int kbase = kbase0 + (t_begin + t) * BN + warp * 16;     // this warp's 16 keys
+        const uint32_t ka = smem_u32(kbuf + (t % STAGES) * TILE_BYTES) + warp * 16 * ROWB;
+        const uint32_t va = smem_u32(vbuf + (t % STAGES) * TILE_BYTES) + warp * 16 * ROWB;
+
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        const uint32_t kaddr = ka + ((lane & 7) + (lane >> 4) * 8) * ROWB + ((lane >> 3) & 1) * 16;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t b[4];
+            ldsm_x4(b, kaddr + ks * 32);
+            mma_bf16(s[0], qf[ks], b[0], b[1]);
+            mma_bf16(s[1], qf[ks], b[2], b[3]);
+        }
+        float tmA = -INFINITY, tmB = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int j = kbase + n * 8 + (lane & 3) * 2;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int jj = j + e;
+                const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
+                const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                s[n][e] = a;
+                s[n][2 + e] = b;
+                tmA = fmaxf(tmA, a);
+                tmB = fmaxf(tmB, b);
+            }
+        }
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1));
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
+        const float nmA = fmaxf(mA, tmA), nmB = fmaxf(mB, tmB);
+        const float baseA = nmA == -INFINITY ? 0.f : nmA, baseB = nmB == -INFINITY ? 0.f : nmB;
+        const float cA = fast_exp2(mA - baseA), cB = fast_exp2(mB - baseB);
+        mA = nmA;
+        mB = nmB;
+        uint32_t pf[4];
+        float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const float p0 = fast_exp2(s[n][0] - baseA), p1 = fast_exp2(s[n][1] - baseA);
+            const float p2 = fast_exp2(s[n][2] - baseB), p3 = fast_exp2(s[n][3] - baseB);
+            sumA += p0 + p1;
+            sumB += p2 + p3;
+            pf[n * 2] = pack_bf16(p0, p1);
+            pf[n * 2 + 1] = pack_bf16(p2, p3);
+        }
+        lA = lA * cA + sumA;
+        lB = lB * cB + sumB;
+        const uint32_t vaddr = va + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+            uint32_t b[4];
+            ldsm_x4_trans(b, vaddr + dp * 32);
+            o[2 * dp][0] *= cA;
+            o[2 * dp][1] *= cA;
+            o[2 * dp][2] *= cB;
+            o[2 * dp][3] *= cB;
+            o[2 * dp + 1][0] *= cA;
+            o[2 * dp + 1][1] *= cA;
+            o[2 * dp + 1][2] *= cB;
+            o[2 * dp + 1][3] *= cB;
+            mma_bf16(o[2 * dp], pf, b[0], b[1]);
+            mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                  // the tiles are no longer read
+
+    // merge the four warps' partial results through shared memory
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    float* m_s = reinterpret_cast<float*>(smem);      // [4][16]
+    float* l_s = m_s + 64;                            // [4][16]
+    float* o_s = l_s + 64;                            // [4][16][HD]
+    if ((lane & 3) == 0) {
+        m_s[warp * 16 + rA] = mA;
+        m_s[warp * 16 + rB] = mB;
+        l_s[warp * 16 + rA] = lA;
+        l_s[warp * 16 + rB] = lB;
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        float* a = o_s + ((size_t)warp * 16 + rA) * HD + n * 8 + (lane & 3) * 2;
+        float* b = o_s + ((size_t)warp * 16 + rB) * HD + n * 8 + (lane & 3) * 2;
+        a[0] = o[n][0];
+        a[1] = o[n][1];
+        b[0] = o[n][2];
+        b[1] = o[n][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * HD; idx += NT) {
+        const int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, m_s[w * 16 + row]);
+        float l = 0.f, acc = 0.f;
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float c = fast_exp2(m_s[w * 16 + row] - m);
+                l += l_s[w * 16 + row] * c;
+                acc += o_s[((size_t)w * 16 + row) * HD + d] * c;
+            }
+        }
+        const float val = l > 0.f ? acc / l : 0.f;
+        const int i = row / P.group, g = row - i * P.group;
+        const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
+        if (P.n_split == 1) {
+            P.out[unit * HD + d] = __float2bfloat16_rn(val);
+        } else {
+            const size_t units = (size_t)P.n_tokens * P.n_heads;
+            P.part_o[((size_t)split * units + unit) * HD + d] = val;
+            if (d == 0)
+                P.part_lse[(size_t)split * units + unit] = l > 0.f ? m + log2f(l) : -INFINITY;
+        }
+    }
+}
+
+// out[unit] = sum_s w_s part_o[s, unit] with w_s = 2^(lse_s - max lse) normalised.
+__global__ void attention_merge_kernel(const Params P) {
+    const int t = blockIdx.x;
+    // only the requests the split kernel took have partial results
+    int r = 0;
+    while (r + 1 < P.n_req && P.cu_q[r + 1] <= t) ++r;
+    if (!is_small(P.cu_q[r + 1] - P.cu_q[r], P.group)) return;
+    const size_t units = (size_t)P.n_tokens * P.n_heads;
+    for (int idx = threadIdx.x; idx < P.n_heads * HD; idx += blockDim.x) {
+        const int h = idx / HD, d = idx - h * HD;
+        const size_t unit = (size_t)t * P.n_heads + h;
+        float m = -INFINITY;
+        for (int s = 0; s < P.n_split; ++s) m = fmaxf(m, P.part_lse[s * units + unit]);
+        float wsum = 0.f, acc = 0.f;
+        if (m != -INFINITY) {
+            for (int s = 0; s < P.n_split; ++s) {
+                const float w = fast_exp2(P.part_lse[s * units + unit] - m);
+                wsum += w;
+                acc += w * P.part_o[(s * units + unit) * HD + d];
+            }
+        }
+        P.out[unit * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+    }
+}
+
+constexpr int TILE_SMEM = 5 * TILE_BYTES;
+constexpr int SPLIT_SMEM_PIPE = 16 * ROWB + 2 * STAGES * TILE_BYTES;
+constexpr int SPLIT_SMEM_MERGE = (128 + 4 * 16 * HD) * 4;
+constexpr int SPLIT_SMEM = SPLIT_SMEM_PIPE > SPLIT_SMEM_MERGE ? SPLIT_SMEM_PIPE : SPLIT_SMEM_MERGE;
+}  // namespace
+
+// n_tiles: 64-row tiles the tile kernel has to run (0: none); n_small: 1 if any
+// request goes to the split kernel.  part_o / part_lse are scratch memory of
+// n_split * T * H * (HD + 1) floats, needed when n_split > 1.
+MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, const void* v_pool,
+                              const int* block_table, int max_blocks, const int* cu_q,
+                              const int* ctx_len, int n_req, int n_tokens, int n_heads, int n_kv,
+                              int block_size, float scale, int window, int n_tiles, int n_small,
+                              int n_split, float* part_o, float* part_lse, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_req <= 0) return 0;
+    if (n_heads % n_kv || n_split < 1 || (n_split > 1 && (!part_o || !part_lse)))
+        return MLS_ERR_UNSUPPORTED;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tile_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attention_split_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SPLIT_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    Params P;
+    P.qkv = (const __nv_bfloat16*)qkv;
+    P.out = (__nv_bfloat16*)out;
+    P.k_pool = (const __nv_bfloat16*)k_pool;
+    P.v_pool = (const __nv_bfloat16*)v_pool;
+    P.block_table = block_table;
+    P.cu_q = cu_q;
+    P.ctx_len = ctx_len;
+    P.part_o = part_o;
+    P.part_lse = part_lse;
+    P.max_blocks = max_blocks;
+    P.n_req = n_req;
+    P.n_tokens = n_tokens;
+    P.n_heads = n_heads;
+    P.n_kv = n_kv;
+    P.group = n_heads / n_kv;
+    P.block_size = block_size;
+    P.window = window;
+    P.n_split = n_split;
+    P.small_only = n_small ? 1 : 0;
+    P.scale_log2 = scale * LOG2E;
+    if (n_tiles > 0) {
+        attention_tile_kernel<<<dim3(n_tiles, n_kv), NT, TILE_SMEM, stream>>>(P);
+        int rc = launch_status();
+        if (rc) return rc;
+    }
+    if (n_small) {
+        attention_split_kernel<<<dim3(n_req, n_kv, n_split), NT, SPLIT_SMEM, stream>>>(P);
+        int rc = launch_status();
+        if (rc) return rc;
+        if (n_split > 1) {
+            attention_merge_kernel<<<n_tokens, 128, 0, stream>>>(P);
+            rc = launch_status();
+            if (rc) return rc;
+        }
+    }
+    return 0;
+}
+
+MLS_API int mls_attention_head_dim() { return HD; }

@@ -86,6 +86,7 @@ class Ops:
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
+        self._scratch: dict = {}
         self._gemm = None
         self.attention_impl = os.environ.get("MLS_B200_ATTENTION", "auto")
         self.gemm_impl = os.environ.get("MLS_B200_GEMM", "auto")
@@ -93,6 +94,14 @@ class Ops:
         self.library_launches = 0    # plain matrix products handed to the library
 
     # ------------------------------------------------------------------ helpers
+    def scratch(self, tag: str, n_floats: int):
+        """Float32 scratch memory that lives as long as the kernels' owner."""
+        buf = self._scratch.get(tag)
+        if buf is None or buf.numel() < n_floats:
+            buf = torch.empty(max(n_floats, 1 << 16), dtype=torch.float32, device=self.device)
+            self._scratch[tag] = buf
+        return buf
+
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
@@ -197,6 +206,38 @@ class Ops:
         """Make sure attention kernels for this head size exist, or say why not."""
         _need(hd % 16 == 0 and 16 <= hd <= 256,
               f"attention kernels take head sizes 16..256 in steps of 16, not {hd}")
+        if self.act_dtype == torch.bfloat16 and hd not in self._attention_libs:
+            lib = library.load("attention", {"MLS_HEAD_DIM": int(hd)})
+            fn = _decl(lib, "mls_attention_mma",
+                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I,
+                        _P, _P, _P])
+            self._attention_libs[hd] = fn
+
+    def _attention_plan(self, step, group: int, n_kv: int) -> tuple:
+        """(64-row tiles, any small request, context splits) for a step: requests
+        whose (token, head) rows of one kv head fit 16 rows go to the split
+        kernel, the context cut so that the GPU's SMs all have work."""
+        key = ("mma", group, n_kv)
+        plan = step.attn_tiles.get(key)
+        if plan is None:
+            small = [q * group <= 16 for q in step.q_lens]
+            n_tiles = sum((q * group + 63) // 64 for q, s in zip(step.q_lens, small) if not s)
+            n_small = sum(small)
+            n_split = 1
+            if n_small:
+                longest = max(c for c, s in zip(step.ctx_lens, small) if s)
+                n_split = self.split_for(n_small, longest, n_kv)
+            plan = (n_tiles, 1 if n_small else 0, n_split)
+            step.attn_tiles[key] = plan
+        return plan
+
+    @staticmethod
+    def split_for(n_small: int, longest: int, n_kv: int) -> int:
+        """Context splits for ``n_small`` decoding requests of up to ``longest`` keys."""
+        ctas = max(1, n_small * n_kv)
+        want = -(-2 * 148 // ctas)                 # two CTAs for every SM
+        most = max(1, longest // 256)              # at least 256 keys a split
+        return max(1, min(want, most, 64))
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
                         scale: float, window: int) -> None:
@@ -204,6 +245,23 @@ class Ops:
         t = step.n_tokens
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
         _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
+        if qkv.dtype == torch.bfloat16 and self.attention_impl != "simt":
+            fn = self._attention_libs.get(hd)
+            _need(fn is not None, f"attention kernels for head size {hd} were not required")
+            n_tiles, n_small, n_split = self._attention_plan(step, n_heads // n_kv, n_kv)
+            part_o = part_lse = None
+            if n_split > 1:
+                units = t * n_heads
+                scratch = self.scratch("attention_partials", n_split * units * (hd + 1))
+                part_o = scratch[:n_split * units * hd]
+                part_lse = scratch[n_split * units * hd:]
+            self.launches += (1 if n_tiles else 0) + (n_small and (2 if n_split > 1 else 1))
+            _check(fn(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
+                      _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
+                      step.n_requests, t, n_heads, n_kv, g.block_size, float(scale), int(window),
+                      n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse), self._stream()),
+                   "attention_mma")
+            return
         self.launches += 1
         _check(self._attention_simt(
             _ptr(qkv), _ptr(out), _code(qkv.dtype), _ptr(cache.k_pool), _ptr(cache.v_pool),

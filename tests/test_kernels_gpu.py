@@ -1,0 +1,370 @@
+"""Each kernel alone against its plain reference, at other sizes than the engine's."""
+
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+from mini_llm_stack_b200.cache.manager import CacheManager
+from mini_llm_stack_b200.engine.batch import BatchBuilder, Entry
+from mini_llm_stack_b200.ops.kernels import KernelError, Runtime
+from mini_llm_stack_b200.parts.base import CacheHandle, PagedKV
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def rts():
+    return {dt: Runtime(DEV, dt) for dt in DTYPES}
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# --------------------------------------------------------------------------- embed
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab, d", [(97, 96), (1000, 4097), (5, 8)])
+def test_embed(rts, dtype, vocab, d):
+    ops = rts[dtype].ops
+    table = rand((vocab, d), dtype, 1)
+    ids = torch.randint(0, vocab, (37,), generator=torch.Generator().manual_seed(2)).int().to(DEV)
+    x = torch.empty((37, d), dtype=torch.float32, device=DEV)
+    ops.embed(ids, table, x, vocab)
+    assert torch.equal(x, table.float()[ids.long()])
+    ops.check_status()
+    ops.embed(torch.tensor([vocab], dtype=torch.int32, device=DEV), table, x[:1], vocab)
+    with pytest.raises(KernelError, match="vocabulary"):
+        ops.check_status()
+
+
+# ---------------------------------------------------------------------------- norm
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, d, eps", [(5, 96, 1e-6), (33, 4096, 1e-5), (2, 1000, 3e-5),
+                                          (1, 16, 1e-5), (3, 11008, 1e-5)])
+def test_add_rmsnorm(rts, dtype, rows, d, eps):
+    ops = rts[dtype].ops
+    x = rand((rows, d), torch.float32, 3, 2.0)
+    delta = rand((rows, d), dtype, 4)
+    w = 1 + rand((d,), dtype, 5, 0.1)
+    h = torch.empty((rows, d), dtype=dtype, device=DEV)
+    want_x = x + delta.float()
+    want_h = P.plain_rmsnorm(want_x.cpu(), w.cpu(), eps)
+    xx = x.clone()
+    ops.add_rmsnorm(xx, delta, w, eps, h)
+    assert torch.equal(xx, want_x)                       # the residual sum is exact float32
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    assert torch.allclose(h.float().cpu(), want_h, rtol=tol, atol=tol)
+    # no delta: x is left alone
+    xx = x.clone()
+    ops.add_rmsnorm(xx, None, w, eps, h)
+    assert torch.equal(xx, x)
+    assert torch.allclose(h.float().cpu(), P.plain_rmsnorm(x.cpu(), w.cpu(), eps), rtol=tol, atol=tol)
+    # gathered rows: only those rows, x untouched
+    pick = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    hg = torch.empty((2, d), dtype=dtype, device=DEV)
+    xx = x.clone()
+    ops.gather_add_rmsnorm(xx, delta, pick, 2, w, eps, hg)
+    assert torch.equal(xx, x)
+    assert torch.allclose(hg.float().cpu(), want_h[[rows - 1, 0]], rtol=tol, atol=tol)
+
+
+def test_norm_weight_may_stay_float32_in_a_bfloat16_run(rts):
+    ops = rts[torch.bfloat16].ops
+    x = rand((4, 80), torch.float32, 6)
+    w = 1 + rand((80,), torch.float32, 7, 0.1)
+    h = torch.empty((4, 80), dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(x, None, w, 1e-5, h)
+    assert torch.allclose(h.float().cpu(), P.plain_rmsnorm(x.cpu(), w.cpu(), 1e-5), rtol=8e-3, atol=8e-3)
+
+
+# ------------------------------------------------------------------------ gemm f32
+@pytest.mark.parametrize("m, n, k", [(1, 97, 96), (7, 300, 172), (130, 65, 33), (64, 64, 16),
+                                     (3, 1000, 1023), (257, 129, 4096)])
+def test_gemm_f32_is_true_float32_and_batch_invariant(rts, m, n, k):
+    ops = rts[torch.float32].ops
+    a, w = rand((m, k), torch.float32, 8), rand((n, k), torch.float32, 9)
+    out = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    ops.linear(a, w, out)
+    want = (a.double() @ w.double().t())
+    err = (out.double() - want).abs().max().item()
+    # a float32 running sum over k terms is off by about sqrt(k) roundings of its own
+    # size; products rounded to TF32 (10-bit mantissa) would be off by sqrt(k) * 2^-11
+    # of a product, some fifty times more
+    bound = 4 * math.sqrt(k) * 2.0 ** -24 * want.abs().max().item()
+    assert err <= bound and bound < math.sqrt(k) * 2.0 ** -11 / 5, (err, bound)
+    # a row's result does not depend on what else is in the batch
+    one = torch.empty((1, n), dtype=torch.float32, device=DEV)
+    ops.linear(a[m // 2:m // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one[0], out[m // 2])
+
+
+def test_linear_with_float32_weights_in_a_bfloat16_run(rts):
+    ops = rts[torch.bfloat16].ops
+    a, w = rand((5, 64), torch.bfloat16, 10), rand((24, 64), torch.float32, 11)
+    out = torch.empty((5, 24), dtype=torch.bfloat16, device=DEV)
+    ops.linear(a, w, out)
+    want = (a.float() @ w.t()).to(torch.bfloat16)
+    assert torch.equal(out, want) or torch.allclose(out.float(), want.float(), rtol=1e-2, atol=1e-3)
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 128, 64), (8, 6144, 4096), (37, 257, 200), (300, 96, 1000),
+                                     (64, 1000, 4096), (2048, 512, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_linear_bf16(rts, m, n, k, out_dtype):
+    ops = rts[torch.bfloat16].ops
+    a, w = rand((m, k), torch.bfloat16, 12), rand((n, k), torch.bfloat16, 13, 0.05)
+    out = torch.empty((m, n), dtype=out_dtype, device=DEV)
+    ops.linear(a, ops.prepare_weight(w), out)
+    want = a.float() @ w.float().t()
+    scale = want.abs().max().item()
+    tol = 1e-5 if out_dtype == torch.float32 else 5e-3
+    assert (out.float() - want).abs().max().item() <= tol * scale + 1e-6
+
+
+# ------------------------------------------------------------------------- swiglu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("t, inter", [(3, 172), (17, 14336), (1, 5)])
+def test_swiglu(rts, dtype, t, inter):
+    ops = rts[dtype].ops
+    gu = rand((t, 2 * inter), dtype, 14, 3.0)
+    out = torch.empty((t, inter), dtype=dtype, device=DEV)
+    ops.swiglu(gu, out)
+    g, u = gu.float().cpu()[:, :inter], gu.float().cpu()[:, inter:]
+    want = torch.nn.functional.silu(g) * u
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    assert torch.allclose(out.float().cpu(), want, rtol=tol, atol=tol)
+
+
+# ----------------------------------------------------------------------- sampling
+@pytest.mark.parametrize("vocab", [97, 256, 1000, 128256])
+def test_argmax_and_temperature_sampling(rts, vocab):
+    ops = rts[torch.float32].ops
+    n = 6
+    logits = rand((n, vocab), torch.float32, 15, 2.0)
+    logits[1, vocab // 2] = logits[1].max() + 1
+    logits[2, 3] = logits[2, vocab - 1] = logits[2].max() + 1          # a tie: first wins
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, None, None, out)
+    assert out.tolist() == [int(torch.argmax(r)) for r in logits.cpu()]
+    assert out[2].item() == 3
+    temps = torch.tensor([0.8, 0.0, 1.5, 0.3, 1.0, 0.8], device=DEV)
+    us = torch.tensor([0.0, 0.5, 0.999999, 0.37, 0.81, 0.5], device=DEV)
+    ops.sample(logits, temps, us, out)
+    for i in range(n):
+        want = P.plain_sample(logits[i].cpu(), temps[i].item(), us[i].item())
+        got = out[i].item()
+        if got != want:      # u may sit within rounding of a step of the cumulative sum
+            z = logits[i].cpu() / temps[i].item()
+            cum = torch.cumsum(torch.softmax(z, 0), 0)
+            assert abs(cum[min(got, want)].item() - us[i].item()) < 1e-5, (i, got, want)
+
+
+# ------------------------------------------------------------------ rope and store
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv, hd, theta, block", [(4, 2, 16, 10000.0, 4), (3, 1, 32, 5e5, 8),
+                                                         (5, 5, 48, 25000.0, 16), (8, 2, 128, 5e5, 16)])
+def test_rope_store(rts, dtype, heads, kv, hd, theta, block):
+    ops = rts[dtype].ops
+    max_pos, pages, t = 200, 40, 23
+    cos, sin = P.plain_rotary_tables(hd, max_pos, theta)
+    qkv = rand((t, (heads + 2 * kv) * hd), dtype, 16)
+    pos = torch.randint(0, max_pos, (t,), generator=torch.Generator().manual_seed(17)).int()
+    slots = torch.randperm(pages * block, generator=torch.Generator().manual_seed(18))[:t].int()
+    k_pool = torch.full((pages, kv, block, hd), 7.0, dtype=dtype, device=DEV)
+    v_pool = torch.full((pages, kv, block, hd), 7.0, dtype=dtype, device=DEV)
+    src = qkv.float().cpu()
+    got = qkv.clone()
+    ops.rope_store(got, pos.to(DEV), cos.to(DEV), sin.to(DEV), slots.to(DEV), k_pool, v_pool, t,
+                   heads, kv, hd, max_pos, True)
+    ops.check_status()
+    rnd = P.ident if dtype == torch.float32 else P.to_bf16
+    q = src[:, :heads * hd].view(t, heads, hd).transpose(0, 1)
+    k = src[:, heads * hd:(heads + kv) * hd].view(t, kv, hd).transpose(0, 1)
+    v = src[:, (heads + kv) * hd:].view(t, kv, hd)
+    want_q = rnd(P.plain_rope(q, pos.long(), cos, sin)).transpose(0, 1).reshape(t, heads * hd)
+    want_k = rnd(P.plain_rope(k, pos.long(), cos, sin)).transpose(0, 1)      # [t, kv, hd]
+    assert torch.equal(got.float().cpu()[:, :heads * hd], want_q)
+    kp, vp = k_pool.float().cpu(), v_pool.float().cpu()
+    touched = torch.zeros(pages, block, dtype=torch.bool)
+    for i in range(t):
+        pg, off = int(slots[i]) // block, int(slots[i]) % block
+        assert torch.equal(kp[pg, :, off], want_k[i]) and torch.equal(vp[pg, :, off], v[i])
+        touched[pg, off] = True
+    untouched = ~touched[:, None, :].expand(pages, kv, block)
+    assert bool((kp[untouched] == 7.0).all()) and bool((vp[untouched] == 7.0).all())
+    # a call that reads another call's cache rotates its queries and writes nothing
+    k2 = k_pool.clone()
+    got2 = qkv.clone()
+    ops.rope_store(got2, pos.to(DEV), cos.to(DEV), sin.to(DEV), slots.to(DEV), k_pool, v_pool, t,
+                   heads, kv, hd, max_pos, False)
+    assert torch.equal(k2, k_pool) and torch.equal(got2[:, :heads * hd], got[:, :heads * hd])
+
+
+# ----------------------------------------------------------------------- attention
+class AttnCase:
+    """Requests with given context and portion lengths over a small page pool;
+    keys and values are written into the pages the cache manager hands out."""
+
+    def __init__(self, rt, heads, kv, hd, block, ctxs, q_lens, window=None, pages=None, seed=0,
+                 poison=None):
+        self.rt, self.heads, self.kv, self.hd = rt, heads, kv, hd
+        dtype = rt.act_dtype
+        need = sum((c + block - 1) // block for c in ctxs)
+        pages = pages or need + 3
+        self.cache = CacheManager([PagedKV(kv, hd, window)], pages, block, len(ctxs) + 1,
+                                  max(ctxs) + 8, device=DEV, kv_dtype=dtype)
+        self.handle = self.cache.handles()[0]
+        if poison is not None:
+            self.cache.paged[0].kv.fill_(poison)
+        self.k = [rand((kv, c, hd), dtype, seed + 10 * i + 1) for i, c in enumerate(ctxs)]
+        self.v = [rand((kv, c, hd), dtype, seed + 10 * i + 2) for i, c in enumerate(ctxs)]
+        self.q = [rand((heads, n, hd), dtype, seed + 10 * i + 3) for i, n in enumerate(q_lens)]
+        self.ctxs, self.q_lens, self.window, self.block = ctxs, q_lens, window, block
+
+    def run(self):
+        rt, cache = self.rt, self.cache
+        entries = []
+        for i, (c, n) in enumerate(zip(self.ctxs, self.q_lens)):
+            cache.admit(i)
+            # everything but the portion is already stored; a window gives pages back
+            assert cache.reserve(i, c - n)
+            cache.commit(i, c - n)
+            assert cache.reserve(i, n)
+            entries.append(Entry(i, [0] * n, []))
+        for i, c in enumerate(self.ctxs):
+            pages = cache.pages_of(i)
+            for j in range(c):
+                pg = pages[j // self.block]
+                if pg >= 0:
+                    self.handle.k_pool[pg, :, j % self.block] = self.k[i][:, j]
+                    self.handle.v_pool[pg, :, j % self.block] = self.v[i][:, j]
+        step = BatchBuilder(cache, DEV, 10, 1 << 20).build(entries)
+        t = step.n_tokens
+        width = (self.heads + 2 * self.kv) * self.hd
+        qkv = torch.zeros((t, width), dtype=rt.act_dtype, device=DEV)
+        at = 0
+        for q in self.q:
+            n = q.shape[1]
+            qkv[at:at + n, :self.heads * self.hd] = q.transpose(0, 1).reshape(n, -1)
+            at += n
+        out = torch.empty((t, self.heads * self.hd), dtype=rt.act_dtype, device=DEV)
+        rt.ops.require_attention(self.hd)
+        rt.ops.paged_attention(qkv, out, self.handle, step, self.heads, self.kv, self.hd,
+                               self.hd ** -0.5, self.window or 0)
+        torch.cuda.synchronize()
+        return out.float().cpu()
+
+    def want(self):
+        rows = []
+        for q, k, v in zip(self.q, self.k, self.v):
+            o = P.plain_attention(q.float().cpu(), k.float().cpu(), v.float().cpu(),
+                                  self.hd ** -0.5, self.window)
+            rows.append(o.transpose(0, 1).reshape(q.shape[1], -1))
+        return torch.cat(rows)
+
+
+def attn_tol(dtype, ctx=64):
+    """Largest |difference| as a fraction of the largest output.  float32: a sum
+    over ctx keys is off by about sqrt(ctx) roundings (in the kernel and in the
+    plain reference alike); bfloat16: the probabilities and the output are
+    rounded to 8 bits."""
+    if dtype == torch.float32:
+        return max(2e-6, 4 * math.sqrt(ctx) * 2.0 ** -24)
+    return 1.2e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv, hd, block", [(4, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16),
+                                                  (8, 2, 64, 16), (8, 2, 128, 16), (32, 1, 64, 32),
+                                                  (2, 1, 256, 16), (6, 3, 80, 5)])
+def test_attention_mixed_batch(rts, dtype, heads, kv, hd, block):
+    # whole prompts, portions after cached context, single tokens, together
+    ctxs = [7, 200, 45, 128, 1, 333, 65, 64]
+    q_lens = [7, 1, 45, 3, 1, 70, 1, 64]
+    case = AttnCase(rts[dtype], heads, kv, hd, block, ctxs, q_lens, seed=100 + hd)
+    got, want = case.run(), case.want()
+    assert (got - want).abs().max().item() <= attn_tol(dtype, 333) * want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("ctx", [1, 15, 16, 17, 64, 65, 255, 256, 257, 1000, 3000])
+def test_attention_decode_at_page_and_tile_edges(rts, dtype, ctx):
+    case = AttnCase(rts[dtype], 8, 2, 64, 16, [ctx, max(1, ctx - 1)], [1, 1], seed=ctx)
+    got, want = case.run(), case.want()
+    assert (got - want).abs().max().item() <= attn_tol(dtype, ctx) * want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unused_slots_must_not_leak(rts, dtype):
+    # the reference's poisoned-slot test (tests/test_serving.py:89-108): whatever lies
+    # in the pool beyond a request's keys must not reach the result
+    for q_lens in ([1, 1, 1], [5, 23, 12]):
+        case = AttnCase(rts[dtype], 4, 2, 32, 16, [5, 23, 12], q_lens, seed=9, poison=1e6)
+        got, want = case.run(), case.want()
+        assert torch.isfinite(got).all()
+        assert (got - want).abs().max().item() <= attn_tol(dtype) * want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far, ctx, q_len", [(0, 700, 1), (3, 700, 1), (257, 900, 2), (0, 600, 90),
+                                             (511, 513, 1), (640, 1500, 1)])
+def test_one_far_key_among_hundreds_is_found(rts, dtype, far, ctx, q_len):
+    """Random data would hide a lost key: here one key far back carries all the
+    weight, so the output must be that key's value."""
+    case = AttnCase(rts[dtype], 4, 2, 64, 16, [ctx], [q_len], seed=3)
+    q, k, v = case.q[0], case.k[0], case.v[0]
+    k.mul_(0.05)
+    direction = torch.ones(64, dtype=q.dtype, device=DEV)
+    q[:] = direction * 4
+    k[:, far] = direction * 4                      # score 16 * 64 / 8 = 128 above all others
+    got, want = case.run(), case.want()
+    tol = attn_tol(dtype, ctx)
+    mark = v[:, far].float().cpu().repeat_interleave(2, dim=0).reshape(1, -1)   # [1, H * hd]
+    assert (got - mark).abs().max().item() < 2e-2
+    assert (got - want).abs().max().item() <= tol * want.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window, ctx, q_len", [(10, 50, 1), (16, 64, 1), (40, 200, 30), (33, 100, 100),
+                                                (64, 1000, 1), (5, 300, 17)])
+def test_window_edge(rts, dtype, window, ctx, q_len):
+    """The key just outside the window carries a huge score and a huge value: it
+    must not count; the key just inside must."""
+    case = AttnCase(rts[dtype], 4, 2, 32, 16, [ctx], [q_len], window=window, seed=5)
+    q, k, v = case.q[0], case.k[0], case.v[0]
+    p_last = ctx - 1
+    outside = p_last - window                      # hidden from the last query
+    if outside >= 0:
+        k[:, outside] = q[0, -1] * 3
+        v[:, outside] = 1000.0
+    got, want = case.run(), case.want()
+    assert got[-1].abs().max().item() < 100         # the outside key did not leak in
+    # earlier queries of the portion do see that key: compare row by row
+    row_scale = want.abs().max(dim=1).values.clamp(min=1.0)
+    assert bool(((got - want).abs().max(dim=1).values <= attn_tol(dtype, ctx) * row_scale).all())
+
+
+def test_attention_refuses_head_sizes_it_does_not_have(rts):
+    with pytest.raises(KernelError, match="steps of 16"):
+        rts[torch.bfloat16].ops.require_attention(40)
+    with pytest.raises(KernelError, match="steps of 16"):
+        rts[torch.float32].ops.require_attention(272)
+
+
+def test_bf16_tensor_core_attention_agrees_with_the_plain_kernel(rts):
+    rt = rts[torch.bfloat16]
+    ctxs, q_lens = [500, 77, 1200, 300], [1, 77, 2, 150]
+    a = AttnCase(rt, 8, 2, 128, 16, ctxs, q_lens, seed=21)
+    got = a.run()
+    rt.ops.attention_impl = "simt"
+    try:
+        b = AttnCase(rt, 8, 2, 128, 16, ctxs, q_lens, seed=21)
+        ref = b.run()
+    finally:
+        rt.ops.attention_impl = "auto"
+    assert (got - ref).abs().max().item() <= 1.2e-2 * ref.abs().max().item()
