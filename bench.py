@@ -243,23 +243,28 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
 
     # ---------------------------------------------------- end to end (Engine API)
-    prompt_len = ctx - (warmup + steps) - 1
-    reqs = [engine.submit(rand_tokens(prompt_len), max_new_tokens=warmup + steps + 1)
+    # every request must still be decoding when the last one has finished its
+    # prompt: the first to finish decodes during the others' portions
+    portions = args.batch * (-(-ctx // PREFILL_TOKENS))
+    max_new = portions + warmup + steps + 4
+    prompt_len = ctx - max_new
+    reqs = [engine.submit(rand_tokens(prompt_len), max_new_tokens=max_new)
             for _ in range(args.batch)]
     while any(r.remaining > 1 or not r.generated for r in reqs):
         engine.step()                            # prompts in portions, untimed
     for _ in range(warmup):
         engine.step()
+    assert len(engine.running) == args.batch
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     n0 = sum(len(r.generated) for r in reqs)
-    for _ in range(steps - 1):
+    for _ in range(steps):
         engine.step()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_tokens = sum(len(r.generated) for r in reqs) - n0
+    assert len(engine.running) == args.batch and e2e_tokens == steps * args.batch
     h2d = runner.builder.last_bytes
-    engine.run_until_done()
     clocks.stop()
 
     line = {

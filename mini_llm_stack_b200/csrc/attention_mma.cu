@@ -483,18 +483,18 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
 }
 
 // out[unit] = sum_s w_s part_o[s, unit] with w_s = 2^(lse_s - max lse) normalised.
+// One block per (token, head), one thread per element of the head.
 __global__ void attention_merge_kernel(const Params P) {
-    const int t = blockIdx.x;
+    const int t = blockIdx.x, h = blockIdx.y;
     // only the requests the split kernel took have partial results
     int r = 0;
     while (r + 1 < P.n_req && P.cu_q[r + 1] <= t) ++r;
     if (!is_small(P.cu_q[r + 1] - P.cu_q[r], P.group)) return;
     const size_t units = (size_t)P.n_tokens * P.n_heads;
-    for (int idx = threadIdx.x; idx < P.n_heads * HD; idx += blockDim.x) {
-        const int h = idx / HD, d = idx - h * HD;
-        const size_t unit = (size_t)t * P.n_heads + h;
-        float m = -INFINITY;
-        for (int s = 0; s < P.n_split; ++s) m = fmaxf(m, P.part_lse[s * units + unit]);
+    const size_t unit = (size_t)t * P.n_heads + h;
+    float m = -INFINITY;
+    for (int s = 0; s < P.n_split; ++s) m = fmaxf(m, P.part_lse[s * units + unit]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float wsum = 0.f, acc = 0.f;
         if (m != -INFINITY) {
             for (int s = 0; s < P.n_split; ++s) {
@@ -565,7 +565,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
         int rc = launch_status();
         if (rc) return rc;
         if (n_split > 1) {
-            attention_merge_kernel<<<n_tokens, 128, 0, stream>>>(P);
+            attention_merge_kernel<<<dim3(n_tokens, n_heads), HD < 128 ? HD : 128, 0, stream>>>(P);
             rc = launch_status();
             if (rc) return rc;
         }

@@ -83,11 +83,61 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     // u * total may round past the last cumulative sum: the last token then
     if (threadIdx.x == 0) out[blockIdx.x] = found < 0 ? vocab - 1 : found;
 }
+// Greedy rows only, in two steps so that a few rows still use many SMs: every
+// block finds the maximum of CHUNK logits, then one block a row picks among the
+// chunks (the lower index on ties, as before).
+constexpr int CHUNK = 4096;
+
+__global__ void __launch_bounds__(THREADS)
+argmax_chunks_kernel(const float* __restrict__ logits, float* __restrict__ part_val,
+                     int* __restrict__ part_idx, int vocab, int n_chunks) {
+    __shared__ float vs[THREADS];
+    __shared__ int is[THREADS];
+    const int begin = blockIdx.y * CHUNK;
+    const int len = min(CHUNK, vocab - begin);
+    const float* row = logits + (size_t)blockIdx.x * vocab + begin;
+    const int local = block_argmax(row, len, 1.0f, vs, is);
+    if (threadIdx.x == 0) {
+        part_val[blockIdx.x * n_chunks + blockIdx.y] = row[local];
+        part_idx[blockIdx.x * n_chunks + blockIdx.y] = begin + local;
+    }
+}
+
+__global__ void argmax_pick_kernel(const float* __restrict__ part_val,
+                                   const int* __restrict__ part_idx, int* __restrict__ out,
+                                   int n_chunks) {
+    // one warp a row; chunks are in index order, so the first maximum wins
+    const float* v = part_val + (size_t)blockIdx.x * n_chunks;
+    const int* ix = part_idx + (size_t)blockIdx.x * n_chunks;
+    float best = -INFINITY;
+    int idx = NONE;
+    for (int c = threadIdx.x; c < n_chunks; c += 32) {
+        const float x = v[c];
+        if (x > best || (idx == NONE && x == best)) { best = x; idx = ix[c]; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (b2 > best || (b2 == best && i2 < idx)) { best = b2; idx = i2; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = idx == NONE ? 0 : idx;
+}
 }  // namespace
 
+// scratch: n_rows * ceil(vocab / 4096) * 2 words, used by the all-greedy path
+// (temperature == nullptr); pass nullptr to take the one-block-a-row kernel.
 MLS_API int mls_sample(const float* logits, const float* temperature, const float* uniform,
-                       int* out, int n_rows, int vocab, cudaStream_t stream) {
+                       int* out, int n_rows, int vocab, float* scratch, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (temperature == nullptr && scratch != nullptr && vocab > CHUNK) {
+        const int n_chunks = (vocab + CHUNK - 1) / CHUNK;
+        float* part_val = scratch;
+        int* part_idx = reinterpret_cast<int*>(scratch + (size_t)n_rows * n_chunks);
+        argmax_chunks_kernel<<<dim3(n_rows, n_chunks), THREADS, 0, stream>>>(
+            logits, part_val, part_idx, vocab, n_chunks);
+        argmax_pick_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, out, n_chunks);
+        return launch_status();
+    }
     sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, temperature, uniform, out, vocab);
     return launch_status();
 }

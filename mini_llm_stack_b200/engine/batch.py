@@ -47,6 +47,7 @@ class BatchBuilder:
         self._events = [None, None]
         self._turn = 0
         self._dev = None
+        self.generation = 0           # grows when the device buffer moves
         self.last_bytes = 0           # bytes of the last step's host-to-device copy
 
     def _staging(self, n: int):
@@ -60,6 +61,7 @@ class BatchBuilder:
             self._events[i].synchronize()      # the copy that last read this buffer is done
         if self._dev is None or self._dev.numel() < n:
             self._dev = torch.empty(max(n, 1 << 14), dtype=torch.int32, device=self.device)
+            self.generation += 1
         return i, self._pinned[i]
 
     def build(self, entries: list) -> StepContext:

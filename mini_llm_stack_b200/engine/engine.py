@@ -19,10 +19,11 @@ from .scheduler import Scheduler
 
 class Engine:
     def __init__(self, model, num_blocks: int = 256, block_size: int = 16, max_batch: int = 16,
-                 max_tokens_per_step: int = 2048, chunk_size: int = 2048):
+                 max_tokens_per_step: int = 2048, chunk_size: int = 2048,
+                 cuda_graphs: bool = True):
         self.model = model
         self.runner = ModelRunner(model, num_blocks=num_blocks, block_size=block_size,
-                                  max_requests=max_batch)
+                                  max_requests=max_batch, cuda_graphs=cuda_graphs)
         self.cache = self.runner.cache
         self.max_seq_len = model.config.max_seq_len
         self.scheduler = Scheduler(self.cache, max_batch, max_tokens_per_step, chunk_size,

@@ -75,8 +75,11 @@ def random_model(config, seed: int, norm_std: float = 0.0, dtype: str | None = N
 class ModelRunner:
     """A bound model, its cache and the step function over both."""
 
-    def __init__(self, model, num_blocks: int, block_size: int = 16, max_requests: int = 16):
+    def __init__(self, model, num_blocks: int, block_size: int = 16, max_requests: int = 16,
+                 cuda_graphs: bool = True):
         self.model = model
+        self.cuda_graphs = cuda_graphs
+        self._graphs: dict = {}
         self.runtime = model.runtime
         cfg = model.config
         self.cache = CacheManager(
@@ -109,10 +112,44 @@ class ModelRunner:
         the requests' lengths advance once, after the last layer.
         """
         ctx = self.builder.build(entries)
-        logits = self.model.forward(ctx, self.handles)
+        if self.cuda_graphs and ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens:
+            logits = self._decode_from_graph(ctx)
+        else:
+            logits = self.model.forward(ctx, self.handles)
         for e in entries:
             self.cache.commit(e.owner, len(e.tokens))
         self.steps += 1
+        return logits
+
+    def _decode_from_graph(self, ctx):
+        """A step of single decoded tokens, replayed from a CUDA graph.
+
+        Such a step launches the same kernels with the same arguments whenever
+        the number of requests and the cut of the context are the same; only
+        the arrays the batch builder has just copied to the device differ, and
+        they lie at the same addresses.  The first step of a kind runs eagerly
+        (which sizes every buffer), the second is captured, later ones replay.
+        """
+        ops = self.runtime.ops
+        moved = (ops.generation, self.builder.generation)
+        if moved != self._graphs.get("moved"):
+            self._graphs = {"moved": moved}      # a buffer moved: the old graphs are stale
+        key = (ctx.n_requests, ops.decode_graph_key(ctx))
+        entry = self._graphs.get(key)
+        if entry is None:
+            self._graphs[key] = "warm"
+            return self.model.forward(ctx, self.handles)
+        if entry == "warm":
+            before = (ops.launches, ops.library_launches)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.handles)
+            entry = (graph, logits, ops.launches - before[0], ops.library_launches - before[1])
+            self._graphs[key] = entry
+        graph, logits, own, lib = entry
+        graph.replay()
+        ops.launches += own
+        ops.library_launches += lib
         return logits
 
     def release(self, owner) -> None:

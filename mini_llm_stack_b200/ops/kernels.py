@@ -83,13 +83,15 @@ class Ops:
                                      [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _I, _P])
         self._swiglu = _decl(core, "mls_swiglu", [_P, _P, _I, _I, _I, _P])
-        self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P])
+        self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
+        self._attention_shapes: set = set()      # (kv heads, group size) of the mixers
         self._scratch: dict = {}
         self._gemm = None
         self.attention_impl = os.environ.get("MLS_B200_ATTENTION", "auto")
         self.gemm_impl = os.environ.get("MLS_B200_GEMM", "auto")
+        self.generation = 0          # grows whenever a buffer kernels were given moves
         self.launches = 0            # launches of this package's own kernels
         self.library_launches = 0    # plain matrix products handed to the library
 
@@ -100,6 +102,7 @@ class Ops:
         if buf is None or buf.numel() < n_floats:
             buf = torch.empty(max(n_floats, 1 << 16), dtype=torch.float32, device=self.device)
             self._scratch[tag] = buf
+            self.generation += 1
         return buf
 
     def _stream(self):
@@ -202,10 +205,12 @@ class Ops:
                                 pages * block, 1 if writes else 0, _ptr(self.status),
                                 self._stream()), "rope_store")
 
-    def require_attention(self, hd: int) -> None:
+    def require_attention(self, hd: int, n_heads: int = 0, n_kv: int = 0) -> None:
         """Make sure attention kernels for this head size exist, or say why not."""
         _need(hd % 16 == 0 and 16 <= hd <= 256,
               f"attention kernels take head sizes 16..256 in steps of 16, not {hd}")
+        if n_kv:
+            self._attention_shapes.add((n_kv, n_heads // n_kv))
         if self.act_dtype == torch.bfloat16 and hd not in self._attention_libs:
             lib = library.load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
@@ -231,13 +236,38 @@ class Ops:
             step.attn_tiles[key] = plan
         return plan
 
+    def decode_graph_key(self, step) -> tuple:
+        """What, besides the number of requests, fixes the launches of a step of
+        single tokens: the number of context splits of the attention kernel."""
+        if self.act_dtype != torch.bfloat16 or self.attention_impl == "simt":
+            return ()
+        return tuple(sorted((k, v) for k, v in self._split_keys(step).items()))
+
+    def _split_keys(self, step) -> dict:
+        out = {}
+        for (n_kv, group) in self._attention_shapes:
+            out[(n_kv, group)] = self._attention_plan(step, group, n_kv)[2]
+        return out
+
     @staticmethod
     def split_for(n_small: int, longest: int, n_kv: int) -> int:
-        """Context splits for ``n_small`` decoding requests of up to ``longest`` keys."""
-        ctas = max(1, n_small * n_kv)
-        want = -(-2 * 148 // ctas)                 # two CTAs for every SM
-        most = max(1, longest // 256)              # at least 256 keys a split
-        return max(1, min(want, most, 64))
+        """Context splits for ``n_small`` decoding requests of up to ``longest`` keys.
+
+        Two CTAs of the split kernel fit an SM, so 296 run at a time; the cost of
+        a choice is its number of such waves times the 64-key tiles a CTA walks
+        (plus two tiles' worth of start-up and merge).  The cheapest choice wins;
+        a split is never shorter than 256 keys.
+        """
+        slots = 2 * 148
+        pairs = max(1, n_small * n_kv)
+        tiles = -(-longest // 64)
+        best, best_cost = 1, None
+        for s in range(1, max(1, min(64, longest // 256)) + 1):
+            waves = -(-pairs * s // slots)
+            cost = waves * (-(-tiles // s) + 2)
+            if best_cost is None or cost < best_cost:
+                best, best_cost = s, cost
+        return best
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
                         scale: float, window: int) -> None:
@@ -286,9 +316,12 @@ class Ops:
         if temperature is not None:
             _need(temperature.dtype == torch.float32 and uniform.dtype == torch.float32,
                   "sample: temperature and uniform must be float32")
-        self.launches += 1
+        scratch = None
+        if temperature is None and v > 4096:
+            scratch = self.scratch("argmax_chunks", 2 * n * ((v + 4095) // 4096))
+        self.launches += 2 if scratch is not None else 1
         _check(self._sample(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), n, v,
-                            self._stream()), "sample")
+                            _ptr(scratch), self._stream()), "sample")
 
 
 class Runtime:
@@ -313,4 +346,5 @@ class Runtime:
         if flat is None or flat.numel() < n:
             flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[key] = flat
+            self.ops.generation += 1       # captured graphs point at the old memory
         return flat[:n].view(shape)

@@ -48,7 +48,7 @@ class GroupedQueryAttention(Mixer):
         self.wqkv = runtime.ops.prepare_weight(torch.cat(parts, dim=0))
         self.wo = runtime.ops.prepare_weight(tensors["wo.weight"])
         self.position.bind({}, runtime)
-        runtime.ops.require_attention(self.head_dim)
+        runtime.ops.require_attention(self.head_dim, self.n_heads, self.n_kv_heads)
 
     def forward(self, h, step: StepContext, cache: CacheHandle):
         rt = self.runtime
