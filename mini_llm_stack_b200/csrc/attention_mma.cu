@@ -18,6 +18,10 @@
 //                          results go to scratch memory and are merged by
 //  attention_merge_kernel.
 #include "common.cuh"
+#include "tma.cuh"
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #ifndef MLS_HEAD_DIM
 #error "compile with -DMLS_HEAD_DIM=<head size>"
@@ -47,6 +51,7 @@ struct Params {
     int max_blocks, n_req, n_tokens, n_heads, n_kv, group, block_size, window, n_split;
     int small_only;                      // tile kernel: 1 = skip requests the split kernel takes
     float scale_log2;                    // scale * log2(e)
+    int* status;                         // device status word (a bounded wait that ran out)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -507,6 +512,313 @@ __global__ void attention_merge_kernel(const Params P) {
     }
 }
 
+
+#if MLS_HEAD_DIM % 64 == 0
+// ----------------------------------------------------------------------------------------
+// The split kernel with the keys and values brought in by TMA: one bulk tensor copy
+// per page and 64-wide half of the head, issued by a producer warp, 128-byte swizzle
+// so that ldmatrix reads without bank conflicts.  Page sizes 8, 16, 32, 64.
+// ----------------------------------------------------------------------------------------
+using namespace mls_tma;
+constexpr int HALVES = HD / 64;
+constexpr int HALF_BYTES = BN * 128;                    // 64 keys x 128 bytes
+constexpr int KV_STAGE = 2 * HALVES * HALF_BYTES;       // keys, then values
+constexpr int TSTAGES = HD <= 128 ? 3 : 2;
+constexpr int TMA_THREADS = 160;                        // 4 consumer warps + 1 producer warp
+
+// address of the 16-byte chunk `chunk` (of the whole head) of key row `row`
+__device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
+    return tile + (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
+                           const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;       // the swizzle needs 1024-byte tiles
+    uint8_t* gbase = smem_raw + (base - raw);
+    const uint32_t q_addr = base + TSTAGES * KV_STAGE;
+    const uint32_t bar0 = q_addr + 16 * ROWB;
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (TSTAGES + s); };
+
+    const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int q_len = P.cu_q[r + 1] - P.cu_q[r];
+    if (!is_small(q_len, P.group)) return;
+    const int rows = q_len * P.group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
+    const int pos0 = ctx - q_len;
+    const int hi = ctx - 1;
+    const int lo = P.window > 0 ? max(0, pos0 - P.window + 1) : 0;
+    const int* table = P.block_table + (size_t)r * P.max_blocks;
+    const int kbase0 = (lo / BN) * BN;
+    const int tiles_all = (hi - kbase0) / BN + 1;
+    const int per = (tiles_all + P.n_split - 1) / P.n_split;
+    const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
+    const int n_tiles = max(0, t_end - t_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TSTAGES; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(empty(s), 4);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ producer
+        const int bs = P.block_size, ppt = BN / bs;
+        const uint32_t page_bytes = bs * 128;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int slot = t % TSTAGES, ph = (t / TSTAGES) & 1;
+            if (!mbar_wait(empty(slot), ph ^ 1)) {
+                if (lane == 0 && P.status) atomicOr(P.status, MLS_STATUS_TIMEOUT);
+                return;
+            }
+            const int kb = kbase0 + (t_begin + t) * BN;
+            const uint32_t stage = base + slot * KV_STAGE;
+            bool valid = false;
+            int page = -1;
+            if (lane < ppt) {
+                const int j0 = kb + lane * bs;
+                if (j0 <= hi && j0 + bs > lo) {
+                    page = table[j0 / bs];
+                    valid = page >= 0;
+                }
+            }
+            const unsigned mask = __ballot_sync(0xffffffffu, valid);
+            const unsigned all = ppt >= 32 ? 0xffffffffu : ((1u << ppt) - 1u);
+            if (mask != all) {
+                // pages that are not keys of this request read as zeros
+                for (int pi = 0; pi < ppt; ++pi) {
+                    if ((mask >> pi) & 1u) continue;
+                    for (int part = 0; part < 2 * HALVES; ++part) {
+                        const uint32_t dst = stage + part * HALF_BYTES + pi * page_bytes;
+                        for (uint32_t o = lane * 16; o < page_bytes; o += 512)
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(dst + o),
+                                         "r"(0u) : "memory");
+                    }
+                }
+                fence_proxy_async();
+            }
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_expect_tx(full(slot), __popc(mask) * page_bytes * 2 * HALVES);
+            __syncwarp();
+            if (valid) {
+                const int y = (page * P.n_kv + kvh) * bs;
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    tma_load_2d(stage + h * HALF_BYTES + lane * page_bytes, &kmap, h * 64, y,
+                                full(slot));
+                    tma_load_2d(stage + (HALVES + h) * HALF_BYTES + lane * page_bytes, &vmap,
+                                h * 64, y, full(slot));
+                }
+            }
+        }
+        return;
+    }
+
+    // --------------------------------------------------------------------- consumers
+    const int rA = lane >> 2, rB = rA + 8;
+    const int pA = rA < rows ? pos0 + rA / P.group : -1;
+    const int pB = rB < rows ? pos0 + rB / P.group : -1;
+    const int loA = P.window > 0 ? pA - P.window + 1 : 0;
+    const int loB = P.window > 0 ? pB - P.window + 1 : 0;
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+    uint32_t qf[HD / 16][4];
+
+    if (n_tiles > 0) {
+        // the queries: plain asynchronous copies into a padded tile, then registers
+        const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
+        for (int idx = threadIdx.x; idx < 16 * KCH; idx += 128) {
+            const int rr = idx / KCH, ch = idx - rr * KCH;
+            const bool ok = rr < rows;
+            size_t off = 0;
+            if (ok) {
+                const int i = rr / P.group, g = rr - i * P.group;
+                off = (size_t)(tok0 + i) * row_w + (size_t)(kvh * P.group + g) * HD + ch * 8;
+            }
+            cp_async16(q_addr + rr * ROWB + ch * 16, P.qkv + off, ok);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        const uint32_t qa = q_addr + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) ldsm_x4(qf[ks], qa + ks * 32);
+    }
+    const int krow = warp * 16 + (lane & 7) + (lane >> 4) * 8, kch = (lane >> 3) & 1;
+    const int vrow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, vch = lane >> 4;
+    bool timed_out = false;
+    for (int t = 0; t < n_tiles; ++t) {
+        const int slot = t % TSTAGES, ph = (t / TSTAGES) & 1;
+        if (!mbar_wait(full(slot), ph)) {
+            timed_out = true;
+            break;
+        }
+        const uint32_t ktile = base + slot * KV_STAGE;
+        const uint32_t vtile = ktile + HALVES * HALF_BYTES;
+        const int kbase = kbase0 + (t_begin + t) * BN + warp * 16;
+
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t b[4];
+            ldsm_x4(b, swz(ktile, krow, ks * 2 + kch));
+            mma_bf16(s[0], qf[ks], b[0], b[1]);
+            mma_bf16(s[1], qf[ks], b[2], b[3]);
+        }
+        float tmA = -INFINITY, tmB = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const int j = kbase + n * 8 + (lane & 3) * 2;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int jj = j + e;
+                const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
+                const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                s[n][e] = a;
+                s[n][2 + e] = b;
+                tmA = fmaxf(tmA, a);
+                tmB = fmaxf(tmB, b);
+            }
+        }
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1));
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
+        const float nmA = fmaxf(mA, tmA), nmB = fmaxf(mB, tmB);
+        const float baseA = nmA == -INFINITY ? 0.f : nmA, baseB = nmB == -INFINITY ? 0.f : nmB;
+        const float cA = fast_exp2(mA - baseA), cB = fast_exp2(mB - baseB);
+        mA = nmA;
+        mB = nmB;
+        uint32_t pf[4];
+        float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const float p0 = fast_exp2(s[n][0] - baseA), p1 = fast_exp2(s[n][1] - baseA);
+            const float p2 = fast_exp2(s[n][2] - baseB), p3 = fast_exp2(s[n][3] - baseB);
+            sumA += p0 + p1;
+            sumB += p2 + p3;
+            pf[n * 2] = pack_bf16(p0, p1);
+            pf[n * 2 + 1] = pack_bf16(p2, p3);
+        }
+        lA = lA * cA + sumA;
+        lB = lB * cB + sumB;
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+            uint32_t b[4];
+            ldsm_x4_trans(b, swz(vtile, vrow, dp * 2 + vch));
+            o[2 * dp][0] *= cA;
+            o[2 * dp][1] *= cA;
+            o[2 * dp][2] *= cB;
+            o[2 * dp][3] *= cB;
+            o[2 * dp + 1][0] *= cA;
+            o[2 * dp + 1][1] *= cA;
+            o[2 * dp + 1][2] *= cB;
+            o[2 * dp + 1][3] *= cB;
+            mma_bf16(o[2 * dp], pf, b[0], b[1]);
+            mma_bf16(o[2 * dp + 1], pf, b[2], b[3]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty(slot));
+    }
+    // a wait that ran out is recorded; the warp still joins the barriers below so
+    // that no other warp waits for it (the host raises on the status word)
+    if (timed_out && lane == 0 && P.status) atomicOr(P.status, MLS_STATUS_TIMEOUT);
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");     // every tile has been read
+
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    float* m_s = reinterpret_cast<float*>(gbase);     // [4][16]
+    float* l_s = m_s + 64;                            // [4][16]
+    float* o_s = l_s + 64;                            // [4][16][HD]
+    if ((lane & 3) == 0) {
+        m_s[warp * 16 + rA] = mA;
+        m_s[warp * 16 + rB] = mB;
+        l_s[warp * 16 + rA] = lA;
+        l_s[warp * 16 + rB] = lB;
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        float* a = o_s + ((size_t)warp * 16 + rA) * HD + n * 8 + (lane & 3) * 2;
+        float* b = o_s + ((size_t)warp * 16 + rB) * HD + n * 8 + (lane & 3) * 2;
+        a[0] = o[n][0];
+        a[1] = o[n][1];
+        b[0] = o[n][2];
+        b[1] = o[n][3];
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    for (int idx = threadIdx.x; idx < rows * HD; idx += 128) {
+        const int row = idx / HD, d = idx - row * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, m_s[w * 16 + row]);
+        float l = 0.f, acc = 0.f;
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float c = fast_exp2(m_s[w * 16 + row] - m);
+                l += l_s[w * 16 + row] * c;
+                acc += o_s[((size_t)w * 16 + row) * HD + d] * c;
+            }
+        }
+        const float val = l > 0.f ? acc / l : 0.f;
+        const int i = row / P.group, g = row - i * P.group;
+        const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
+        if (P.n_split == 1) {
+            P.out[unit * HD + d] = __float2bfloat16_rn(val);
+        } else {
+            const size_t units = (size_t)P.n_tokens * P.n_heads;
+            P.part_o[((size_t)split * units + unit) * HD + d] = val;
+            if (d == 0)
+                P.part_lse[(size_t)split * units + unit] = l > 0.f ? m + log2f(l) : -INFINITY;
+        }
+    }
+}
+
+constexpr int TMA_SMEM_PIPE = TSTAGES * KV_STAGE + 16 * ROWB + 16 * TSTAGES + 1024;
+constexpr int TMA_SMEM_MERGE = (128 + 4 * 16 * HD) * 4 + 1024;
+constexpr int TMA_SMEM = TMA_SMEM_PIPE > TMA_SMEM_MERGE ? TMA_SMEM_PIPE : TMA_SMEM_MERGE;
+
+// Tensor maps of the pools, made once per (pool, size) and kept.
+struct MapKey {
+    const void* ptr;
+    long long rows;
+    int block;
+    bool operator<(const MapKey& o) const {
+        return std::tie(ptr, rows, block) < std::tie(o.ptr, o.rows, o.block);
+    }
+};
+static std::map<MapKey, CUtensorMap> g_maps;
+static std::mutex g_maps_lock;
+
+static bool pool_map(const void* pool, long long pool_rows, int block, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_maps_lock);
+    MapKey key{pool, pool_rows, block};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        CUtensorMap m;
+        if (!make_map_bf16_2d(&m, pool, HD, (uint64_t)pool_rows, (uint64_t)HD * 2, 64, block))
+            return false;
+        it = g_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return true;
+}
+#endif  // MLS_HEAD_DIM % 64 == 0
+
 constexpr int TILE_SMEM = 5 * TILE_BYTES;
 constexpr int SPLIT_SMEM_PIPE = 16 * ROWB + 2 * STAGES * TILE_BYTES;
 constexpr int SPLIT_SMEM_MERGE = (128 + 4 * 16 * HD) * 4;
@@ -520,7 +832,8 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
                               const int* block_table, int max_blocks, const int* cu_q,
                               const int* ctx_len, int n_req, int n_tokens, int n_heads, int n_kv,
                               int block_size, float scale, int window, int n_tiles, int n_small,
-                              int n_split, float* part_o, float* part_lse, cudaStream_t stream) {
+                              int n_split, float* part_o, float* part_lse, long long pool_pages,
+                              int* status, int use_tma, cudaStream_t stream) {
     if (n_tokens <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv || n_split < 1 || (n_split > 1 && (!part_o || !part_lse)))
         return MLS_ERR_UNSUPPORTED;
@@ -555,13 +868,37 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     P.n_split = n_split;
     P.small_only = n_small ? 1 : 0;
     P.scale_log2 = scale * LOG2E;
+    P.status = status;
     if (n_tiles > 0) {
         attention_tile_kernel<<<dim3(n_tiles, n_kv), NT, TILE_SMEM, stream>>>(P);
         int rc = launch_status();
         if (rc) return rc;
     }
     if (n_small) {
-        attention_split_kernel<<<dim3(n_req, n_kv, n_split), NT, SPLIT_SMEM, stream>>>(P);
+        bool launched = false;
+#if MLS_HEAD_DIM % 64 == 0
+        if (use_tma && (block_size == 8 || block_size == 16 || block_size == 32 ||
+                        block_size == 64)) {
+            static bool tma_configured = false;
+            if (!tma_configured) {
+                cudaError_t e = cudaFuncSetAttribute(attention_split_tma_kernel,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     TMA_SMEM);
+                if (e != cudaSuccess) return (int)e;
+                tma_configured = true;
+            }
+            CUtensorMap kmap, vmap;
+            const long long rows = pool_pages * n_kv * block_size;
+            if (!pool_map(k_pool, rows, block_size, &kmap) ||
+                !pool_map(v_pool, rows, block_size, &vmap))
+                return MLS_ERR_TENSOR_MAP;
+            attention_split_tma_kernel<<<dim3(n_req, n_kv, n_split), TMA_THREADS, TMA_SMEM,
+                                         stream>>>(P, kmap, vmap);
+            launched = true;
+        }
+#endif
+        if (!launched)
+            attention_split_kernel<<<dim3(n_req, n_kv, n_split), NT, SPLIT_SMEM, stream>>>(P);
         int rc = launch_status();
         if (rc) return rc;
         if (n_split > 1) {

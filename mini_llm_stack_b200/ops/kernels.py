@@ -22,7 +22,8 @@ _I = ctypes.c_int
 _F = ctypes.c_float
 _LL = ctypes.c_longlong
 
-_ERRORS = {100001: "a size this kernel does not support"}
+_ERRORS = {100001: "a size this kernel does not support",
+           100002: "the driver refused to encode a tensor map"}
 
 
 class KernelError(RuntimeError):
@@ -115,7 +116,8 @@ class Ops:
             self.status.zero_()
             what = [n for b, n in ((1, "a token id outside the vocabulary"),
                                    (2, "a position outside the rotary table"),
-                                   (4, "a cache slot outside the pool")) if code & b]
+                                   (4, "a cache slot outside the pool"),
+                                   (8, "a bounded wait inside a kernel ran out")) if code & b]
             raise KernelError("a kernel refused its input: " + "; ".join(what))
 
     # ------------------------------------------------------------------ kernels
@@ -215,7 +217,7 @@ class Ops:
             lib = library.load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I,
-                        _P, _P, _P])
+                        _P, _P, _LL, _P, _I, _P])
             self._attention_libs[hd] = fn
 
     def _attention_plan(self, step, group: int, n_kv: int) -> tuple:
@@ -289,7 +291,9 @@ class Ops:
             _check(fn(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
                       _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                       step.n_requests, t, n_heads, n_kv, g.block_size, float(scale), int(window),
-                      n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse), self._stream()),
+                      n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse),
+                      cache.k_pool.shape[0], _ptr(self.status),
+                      0 if self.attention_impl == "no_tma" else 1, self._stream()),
                    "attention_mma")
             return
         self.launches += 1

@@ -356,15 +356,22 @@ def test_attention_refuses_head_sizes_it_does_not_have(rts):
         rts[torch.float32].ops.require_attention(272)
 
 
-def test_bf16_tensor_core_attention_agrees_with_the_plain_kernel(rts):
+@pytest.mark.parametrize("block", [8, 16, 32, 64])
+def test_bf16_attention_kernels_agree_with_each_other(rts, block):
+    """Tensor cores with TMA loads, tensor cores with plain asynchronous copies,
+    and the CUDA-core kernel, on the same pages."""
     rt = rts[torch.bfloat16]
-    ctxs, q_lens = [500, 77, 1200, 300], [1, 77, 2, 150]
-    a = AttnCase(rt, 8, 2, 128, 16, ctxs, q_lens, seed=21)
-    got = a.run()
-    rt.ops.attention_impl = "simt"
+    ctxs, q_lens = [500, 77, 1200, 300, 2100], [1, 77, 2, 150, 1]
+    got = {}
     try:
-        b = AttnCase(rt, 8, 2, 128, 16, ctxs, q_lens, seed=21)
-        ref = b.run()
+        for impl in ("auto", "no_tma", "simt"):
+            rt.ops.attention_impl = impl
+            got[impl] = AttnCase(rt, 8, 2, 128, block, ctxs, q_lens, seed=21).run()
     finally:
         rt.ops.attention_impl = "auto"
-    assert (got - ref).abs().max().item() <= 1.2e-2 * ref.abs().max().item()
+    rt.ops.check_status()
+    scale = got["simt"].abs().max().item()
+    assert (got["auto"] - got["simt"]).abs().max().item() <= 1.2e-2 * scale
+    assert (got["no_tma"] - got["simt"]).abs().max().item() <= 1.2e-2 * scale
+    # the two tensor-core kernels do the same arithmetic on the same tiles
+    assert (got["auto"] - got["no_tma"]).abs().max().item() <= 1e-3 * scale
