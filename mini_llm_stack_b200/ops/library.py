@@ -40,6 +40,7 @@ MODULES = {
              "attention_simt.cu", "sampling.cu"],
     "attention": ["attention_mma.cu"],
     "gemm": ["gemm_tcgen05.cu"],
+    "argmax_static": ["argmax_static.cu"],
 }
 
 
@@ -50,6 +51,7 @@ def all_modules(head_sizes=()) -> list:
         out += [("attention", {"MLS_HEAD_DIM": int(h)}) for h in head_sizes]
     if (CSRC / "gemm_tcgen05.cu").is_file():
         out.append(("gemm", {}))
+    out.append(("argmax_static", {}))
     return out
 
 
@@ -96,7 +98,9 @@ def _build_dir() -> Path:
 def _module_key(name: str, defines: dict) -> tuple:
     sources = MODULES[name]
     h = hashlib.sha256()
-    for f in sorted(CSRC.glob("*.cuh")) + [CSRC / s for s in sources]:
+    own_headers = [CSRC / (Path(s).stem + ".h") for s in sources]
+    for f in (sorted(CSRC.glob("*.cuh")) + [h for h in own_headers if h.is_file()]
+              + [CSRC / s for s in sources]):
         h.update(f.name.encode())
         h.update(f.read_bytes())
     h.update(repr(sorted(defines.items())).encode())
