@@ -8,7 +8,84 @@
 // rows == nullptr: for every row t: x[t] += delta[t] (if delta), h[t] = norm(x[t]).
 // rows != nullptr: for i < n_rows: v = x[rows[i]] + delta[rows[i]], h[i] = norm(v);
 //                  x is not modified.
+//
+// The sum of squares is taken in an order that depends on the row's width only,
+// so a row's result does not depend on the batch it is in.
 #include "common.cuh"
+
+namespace {
+__device__ __forceinline__ float4 load4(const void* base, size_t i, int dtype) {
+    if (dtype == MLS_BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)base + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    return *reinterpret_cast<const float4*>((const float*)base + i);
+}
+__device__ __forceinline__ void store4(void* base, size_t i, int dtype, float4 v) {
+    if (dtype == MLS_BF16) {
+        uint2 raw;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+        h[0] = __floats2bfloat162_rn(v.x, v.y);
+        h[1] = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>((__nv_bfloat16*)base + i) = raw;
+    } else {
+        *reinterpret_cast<float4*>((float*)base + i) = v;
+    }
+}
+
+// d a multiple of 4 and d / 4 <= blockDim.x * VEC: a row lives in registers.
+template <int VEC>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __restrict__ delta,
+                                       int delta_dtype, const void* __restrict__ w, int w_dtype,
+                                       float eps, void* __restrict__ h, int h_dtype, int d,
+                                       const int* __restrict__ rows) {
+    __shared__ float scratch[33];
+    const int out_row = blockIdx.x;
+    const int src_row = rows ? rows[out_row] : out_row;
+    const size_t xoff = (size_t)src_row * d;
+    const bool in_place = rows == nullptr;
+    const int n4 = d >> 2;
+    float4 v[VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < n4) {
+            float4 a = *reinterpret_cast<const float4*>(x + xoff + 4 * c);
+            if (delta) {
+                const float4 b = load4(delta, xoff + 4 * c, delta_dtype);
+                a.x += b.x;
+                a.y += b.y;
+                a.z += b.z;
+                a.w += b.w;
+                if (in_place) *reinterpret_cast<float4*>(x + xoff + 4 * c) = a;
+            }
+            v[k] = a;
+            ss += a.x * a.x;
+            ss += a.y * a.y;
+            ss += a.z * a.z;
+            ss += a.w * a.w;
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(total / (float)d + eps);
+    const size_t hoff = (size_t)out_row * d;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < n4) {
+            const float4 ww = load4(w, 4 * c, w_dtype);
+            float4 y;
+            y.x = (v[k].x * r) * ww.x;
+            y.y = (v[k].y * r) * ww.y;
+            y.z = (v[k].z * r) * ww.z;
+            y.w = (v[k].w * r) * ww.w;
+            store4(h, hoff + 4 * c, h_dtype, y);
+        }
+    }
+}
 
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta,
                                    int delta_dtype, const void* __restrict__ w, int w_dtype,
@@ -38,14 +115,31 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
         store_from_float(h, hoff + i, h_dtype, y);
     }
 }
+}  // namespace
 
 MLS_API int mls_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w,
                             int w_dtype, float eps, void* h, int h_dtype, int n_rows, int d,
                             const int* rows, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (d % 4 == 0 && d / 4 <= 1024 * 4) {
+        const int n4 = d / 4;
+        int threads = 32;
+        while (threads < 1024 && threads < n4) threads <<= 1;
+        const int vec = (n4 + threads - 1) / threads;      // chunks of four per thread: 1..4
+        if (vec <= 1)
+            add_rmsnorm_vec_kernel<1><<<n_rows, threads, 0, stream>>>(
+                x, delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+        else if (vec <= 2)
+            add_rmsnorm_vec_kernel<2><<<n_rows, threads, 0, stream>>>(
+                x, delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+        else
+            add_rmsnorm_vec_kernel<4><<<n_rows, threads, 0, stream>>>(
+                x, delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+        return launch_status();
+    }
     int threads = 32;
     while (threads < 1024 && threads * 4 < d) threads <<= 1;
-    add_rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, delta, delta_dtype, w, w_dtype, eps,
-                                                       h, h_dtype, d, rows);
+    add_rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, delta, delta_dtype, w, w_dtype, eps, h,
+                                                       h_dtype, d, rows);
     return launch_status();
 }
