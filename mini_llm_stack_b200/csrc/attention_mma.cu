@@ -531,6 +531,66 @@ __device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
     return tile + (chunk >> 3) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
+// The producer warp: for every 64-key tile, wait until its stage is free, then
+// bring in the keys and values of the tile's pages with one bulk tensor copy per
+// page and 64-wide half.  Stage `late_slot` (if any) is lent to the consumers at
+// the start and is first free after they have released it once.
+__device__ __forceinline__ void produce_tiles(const Params& P, const CUtensorMap* kmap,
+                                              const CUtensorMap* vmap, const int* table, int kvh,
+                                              int kb_first, int n_tiles, int lo, int hi,
+                                              uint32_t base, uint32_t bar0, int late_slot) {
+    const int lane = threadIdx.x & 31;
+    const int bs = P.block_size, ppt = BN / bs;
+    const uint32_t page_bytes = bs * 128;
+    for (int t = 0; t < n_tiles; ++t) {
+        const int slot = t % TSTAGES, round = t / TSTAGES;
+        const uint32_t full = bar0 + 8u * slot, empty = bar0 + 8u * (TSTAGES + slot);
+        const uint32_t parity = slot == late_slot ? (round & 1) : ((round & 1) ^ 1);
+        if (!mbar_wait(empty, parity)) {
+            if (lane == 0 && P.status) atomicOr(P.status, MLS_STATUS_TIMEOUT);
+            return;
+        }
+        const int kb = kb_first + t * BN;
+        const uint32_t stage = base + slot * KV_STAGE;
+        bool valid = false;
+        int page = -1;
+        if (lane < ppt) {
+            const int j0 = kb + lane * bs;
+            if (j0 <= hi && j0 + bs > lo) {
+                page = table[j0 / bs];
+                valid = page >= 0;
+            }
+        }
+        const unsigned mask = __ballot_sync(0xffffffffu, valid);
+        const unsigned all = ppt >= 32 ? 0xffffffffu : ((1u << ppt) - 1u);
+        if (mask != all) {
+            // pages that are not keys of this request read as zeros
+            for (int pi = 0; pi < ppt; ++pi) {
+                if ((mask >> pi) & 1u) continue;
+                for (int part = 0; part < 2 * HALVES; ++part) {
+                    const uint32_t dst = stage + part * HALF_BYTES + pi * page_bytes;
+                    for (uint32_t o = lane * 16; o < page_bytes; o += 512)
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(dst + o),
+                                     "r"(0u) : "memory");
+                }
+            }
+            fence_proxy_async();
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_expect_tx(full, __popc(mask) * page_bytes * 2 * HALVES);
+        __syncwarp();
+        if (valid) {
+            const int y = (page * P.n_kv + kvh) * bs;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+                tma_load_2d(stage + h * HALF_BYTES + lane * page_bytes, kmap, h * 64, y, full);
+                tma_load_2d(stage + (HALVES + h) * HALF_BYTES + lane * page_bytes, vmap, h * 64, y,
+                            full);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                            const __grid_constant__ CUtensorMap vmap) {
@@ -569,56 +629,8 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
     __syncthreads();
 
     if (warp == 4) {
-        // ------------------------------------------------------------------ producer
-        const int bs = P.block_size, ppt = BN / bs;
-        const uint32_t page_bytes = bs * 128;
-        for (int t = 0; t < n_tiles; ++t) {
-            const int slot = t % TSTAGES, ph = (t / TSTAGES) & 1;
-            if (!mbar_wait(empty(slot), ph ^ 1)) {
-                if (lane == 0 && P.status) atomicOr(P.status, MLS_STATUS_TIMEOUT);
-                return;
-            }
-            const int kb = kbase0 + (t_begin + t) * BN;
-            const uint32_t stage = base + slot * KV_STAGE;
-            bool valid = false;
-            int page = -1;
-            if (lane < ppt) {
-                const int j0 = kb + lane * bs;
-                if (j0 <= hi && j0 + bs > lo) {
-                    page = table[j0 / bs];
-                    valid = page >= 0;
-                }
-            }
-            const unsigned mask = __ballot_sync(0xffffffffu, valid);
-            const unsigned all = ppt >= 32 ? 0xffffffffu : ((1u << ppt) - 1u);
-            if (mask != all) {
-                // pages that are not keys of this request read as zeros
-                for (int pi = 0; pi < ppt; ++pi) {
-                    if ((mask >> pi) & 1u) continue;
-                    for (int part = 0; part < 2 * HALVES; ++part) {
-                        const uint32_t dst = stage + part * HALF_BYTES + pi * page_bytes;
-                        for (uint32_t o = lane * 16; o < page_bytes; o += 512)
-                            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(dst + o),
-                                         "r"(0u) : "memory");
-                    }
-                }
-                fence_proxy_async();
-            }
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive_expect_tx(full(slot), __popc(mask) * page_bytes * 2 * HALVES);
-            __syncwarp();
-            if (valid) {
-                const int y = (page * P.n_kv + kvh) * bs;
-#pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(stage + h * HALF_BYTES + lane * page_bytes, &kmap, h * 64, y,
-                                full(slot));
-                    tma_load_2d(stage + (HALVES + h) * HALF_BYTES + lane * page_bytes, &vmap,
-                                h * 64, y, full(slot));
-                }
-            }
-        }
+        produce_tiles(P, &kmap, &vmap, table, kvh, kbase0 + t_begin * BN, n_tiles, lo, hi, base,
+                      bar0, /*late_slot=*/-1);
         return;
     }
 
@@ -788,6 +800,227 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
     }
 }
 
+// ----------------------------------------------------------------------------------------
+// The tile kernel (64 rows per CTA, 16 per warp) with the same TMA producer.  The
+// queries borrow the last stage until they are in registers.  Tiles are handed out
+// from the end of each request backwards: the last rows see the most keys, and the
+// longest work should start first.
+// ----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(TMA_THREADS)
+attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
+                          const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    const uint32_t bar0 = base + TSTAGES * KV_STAGE;
+    const uint32_t q_addr = base + (TSTAGES - 1) * KV_STAGE;     // lent by the last stage
+    static_assert(64 * ROWB <= KV_STAGE, "the queries must fit one stage");
+
+    int r = 0, tile = blockIdx.x, q_len = 0, rows = 0;
+    for (; r < P.n_req; ++r) {
+        q_len = P.cu_q[r + 1] - P.cu_q[r];
+        rows = q_len * P.group;
+        int tiles = (P.small_only && is_small(q_len, P.group)) ? 0 : (rows + 63) / 64;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (r >= P.n_req) return;
+    tile = (rows + 63) / 64 - 1 - tile;                           // heavy tiles first
+    const int kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
+    const int row0 = tile * 64;
+    const int pos0 = ctx - q_len;
+    const int i_first = row0 / P.group;
+    const int i_last = (min(rows, row0 + 64) - 1) / P.group;
+    const int hi = pos0 + i_last;
+    const int lo = P.window > 0 ? max(0, pos0 + i_first - P.window + 1) : 0;
+    const int* table = P.block_table + (size_t)r * P.max_blocks;
+    const int kbase0 = (lo / BN) * BN;
+    const int n_tiles = (hi - kbase0) / BN + 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TSTAGES; ++s) {
+            mbar_init(bar0 + 8u * s, 1);
+            mbar_init(bar0 + 8u * (TSTAGES + s), 4);
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        produce_tiles(P, &kmap, &vmap, table, kvh, kbase0, n_tiles, lo, hi, base, bar0,
+                      /*late_slot=*/TSTAGES - 1);
+        return;
+    }
+
+    // queries: asynchronous copies into a padded tile, then registers, then the stage is free
+    {
+        const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
+        for (int idx = threadIdx.x; idx < 64 * KCH; idx += 128) {
+            const int rr = idx / KCH, ch = idx - rr * KCH;
+            const int row = row0 + rr;
+            const bool ok = row < rows;
+            size_t off = 0;
+            if (ok) {
+                const int i = row / P.group, g = row - i * P.group;
+                off = (size_t)(tok0 + i) * row_w + (size_t)(kvh * P.group + g) * HD + ch * 8;
+            }
+            cp_async16(q_addr + rr * ROWB + ch * 16, P.qkv + off, ok);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    }
+    uint32_t qf[HD / 16][4];
+    {
+        const uint32_t qa = q_addr + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROWB +
+                            (lane >> 4) * 16;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) ldsm_x4(qf[ks], qa + ks * 32);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar0 + 8u * (TSTAGES + TSTAGES - 1));   // hand the stage back
+
+    const int rA = row0 + warp * 16 + (lane >> 2), rB = rA + 8;
+    const int pA = rA < rows ? pos0 + rA / P.group : -1;
+    const int pB = rB < rows ? pos0 + rB / P.group : -1;
+    const int loA = P.window > 0 ? pA - P.window + 1 : 0;
+    const int loB = P.window > 0 ? pB - P.window + 1 : 0;
+    // keys up to this position are seen by all 16 rows of the warp: no mask needed
+    const int first_row = row0 + warp * 16;
+    const int p_first = first_row < rows ? pos0 + first_row / P.group : -1;
+    const int last_row = min(rows, first_row + 16) - 1;
+    const int lo_last = P.window > 0 ? pos0 + last_row / P.group - P.window + 1 : 0;
+    const bool full_warp = first_row + 16 <= rows;
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+
+    const int krow = (lane & 7) + (lane >> 4) * 8, kch = (lane >> 3) & 1;
+    const int vrow = (lane & 7) + ((lane >> 3) & 1) * 8, vch = lane >> 4;
+    bool timed_out = false;
+    for (int t = 0; t < n_tiles; ++t) {
+        const int slot = t % TSTAGES, ph = (t / TSTAGES) & 1;
+        if (!mbar_wait(bar0 + 8u * slot, ph)) {
+            timed_out = true;
+            break;
+        }
+        const uint32_t ktile = base + slot * KV_STAGE;
+        const uint32_t vtile = ktile + HALVES * HALF_BYTES;
+        const int kbase = kbase0 + t * BN;
+
+        float s[BN / 8][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < BN / 16; ++np) {
+                uint32_t b[4];
+                ldsm_x4(b, swz(ktile, np * 16 + krow, ks * 2 + kch));
+                mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+                mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        float tmA = -INFINITY, tmB = -INFINITY;
+        const bool need_mask = !full_warp || kbase + BN - 1 > p_first || kbase < lo_last;
+        if (need_mask) {
+#pragma unroll
+            for (int n = 0; n < BN / 8; ++n) {
+                const int j = kbase + n * 8 + (lane & 3) * 2;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int jj = j + e;
+                    const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
+                    const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                    s[n][e] = a;
+                    s[n][2 + e] = b;
+                    tmA = fmaxf(tmA, a);
+                    tmB = fmaxf(tmB, b);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    s[n][e] *= P.scale_log2;
+                    s[n][2 + e] *= P.scale_log2;
+                    tmA = fmaxf(tmA, s[n][e]);
+                    tmB = fmaxf(tmB, s[n][2 + e]);
+                }
+            }
+        }
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 1));
+        tmA = fmaxf(tmA, __shfl_xor_sync(0xffffffffu, tmA, 2));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 1));
+        tmB = fmaxf(tmB, __shfl_xor_sync(0xffffffffu, tmB, 2));
+        const float nmA = fmaxf(mA, tmA), nmB = fmaxf(mB, tmB);
+        const float baseA = nmA == -INFINITY ? 0.f : nmA, baseB = nmB == -INFINITY ? 0.f : nmB;
+        const float cA = fast_exp2(mA - baseA), cB = fast_exp2(mB - baseB);
+        mA = nmA;
+        mB = nmB;
+        float sumA = 0.f, sumB = 0.f;
+        uint32_t pf[BN / 16][4];
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+            const float p0 = fast_exp2(s[n][0] - baseA), p1 = fast_exp2(s[n][1] - baseA);
+            const float p2 = fast_exp2(s[n][2] - baseB), p3 = fast_exp2(s[n][3] - baseB);
+            sumA += p0 + p1;
+            sumB += p2 + p3;
+            pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+            pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+        lA = lA * cA + sumA;
+        lB = lB * cB + sumB;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= cA;
+            o[i][1] *= cA;
+            o[i][2] *= cB;
+            o[i][3] *= cB;
+        }
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t b[4];
+                ldsm_x4_trans(b, swz(vtile, kk * 16 + vrow, dp * 2 + vch));
+                mma_bf16(o[2 * dp], pf[kk], b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pf[kk], b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8u * (TSTAGES + slot));
+    }
+    if (timed_out && lane == 0 && P.status) atomicOr(P.status, MLS_STATUS_TIMEOUT);
+
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = half ? rB : rA;
+        if (row >= rows) continue;
+        const int i = row / P.group, g = row - i * P.group;
+        __nv_bfloat16* dst = P.out + (size_t)(tok0 + i) * P.n_heads * HD +
+                             (size_t)(kvh * P.group + g) * HD + (lane & 3) * 2;
+        const float inv = half ? invB : invA;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            *reinterpret_cast<uint32_t*>(dst + n * 8) =
+                pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+        }
+    }
+}
+
+constexpr int TILE_TMA_SMEM = TSTAGES * KV_STAGE + 16 * TSTAGES + 1024;
+
 constexpr int TMA_SMEM_PIPE = TSTAGES * KV_STAGE + 16 * ROWB + 16 * TSTAGES + 1024;
 constexpr int TMA_SMEM_MERGE = (128 + 4 * 16 * HD) * 4 + 1024;
 constexpr int TMA_SMEM = TMA_SMEM_PIPE > TMA_SMEM_MERGE ? TMA_SMEM_PIPE : TMA_SMEM_MERGE;
@@ -869,35 +1102,47 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     P.small_only = n_small ? 1 : 0;
     P.scale_log2 = scale * LOG2E;
     P.status = status;
+    const bool tma_ok = use_tma && (block_size == 8 || block_size == 16 || block_size == 32 ||
+                                    block_size == 64) && (HD % 64 == 0);
+    (void)tma_ok;
+#if MLS_HEAD_DIM % 64 == 0
+    CUtensorMap kmap, vmap;
+    if (tma_ok) {
+        static bool tma_configured = false;
+        if (!tma_configured) {
+            cudaError_t e = cudaFuncSetAttribute(attention_split_tma_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 TMA_SMEM);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(attention_tile_tma_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TILE_TMA_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            tma_configured = true;
+        }
+        const long long rows = pool_pages * n_kv * block_size;
+        if (!pool_map(k_pool, rows, block_size, &kmap) || !pool_map(v_pool, rows, block_size, &vmap))
+            return MLS_ERR_TENSOR_MAP;
+    }
+#endif
     if (n_tiles > 0) {
-        attention_tile_kernel<<<dim3(n_tiles, n_kv), NT, TILE_SMEM, stream>>>(P);
+#if MLS_HEAD_DIM % 64 == 0
+        if (tma_ok)
+            attention_tile_tma_kernel<<<dim3(n_tiles, n_kv), TMA_THREADS, TILE_TMA_SMEM, stream>>>(
+                P, kmap, vmap);
+        else
+#endif
+            attention_tile_kernel<<<dim3(n_tiles, n_kv), NT, TILE_SMEM, stream>>>(P);
         int rc = launch_status();
         if (rc) return rc;
     }
     if (n_small) {
-        bool launched = false;
 #if MLS_HEAD_DIM % 64 == 0
-        if (use_tma && (block_size == 8 || block_size == 16 || block_size == 32 ||
-                        block_size == 64)) {
-            static bool tma_configured = false;
-            if (!tma_configured) {
-                cudaError_t e = cudaFuncSetAttribute(attention_split_tma_kernel,
-                                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     TMA_SMEM);
-                if (e != cudaSuccess) return (int)e;
-                tma_configured = true;
-            }
-            CUtensorMap kmap, vmap;
-            const long long rows = pool_pages * n_kv * block_size;
-            if (!pool_map(k_pool, rows, block_size, &kmap) ||
-                !pool_map(v_pool, rows, block_size, &vmap))
-                return MLS_ERR_TENSOR_MAP;
+        if (tma_ok)
             attention_split_tma_kernel<<<dim3(n_req, n_kv, n_split), TMA_THREADS, TMA_SMEM,
                                          stream>>>(P, kmap, vmap);
-            launched = true;
-        }
+        else
 #endif
-        if (!launched)
             attention_split_kernel<<<dim3(n_req, n_kv, n_split), NT, SPLIT_SMEM, stream>>>(P);
         int rc = launch_status();
         if (rc) return rc;
