@@ -183,11 +183,46 @@ class Ops:
             return
         _need(w.dtype == torch.bfloat16, f"linear: weight dtype {w.dtype}")
         a16 = a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
+        if self._use_own_gemm(m, n, k):
+            self._gemm_bf16(a16, w, out, m, n, k)
+            return
         self.library_launches += 1
         if out.dtype == torch.float32:
             torch.mm(a16, w.t(), out_dtype=torch.float32, out=out)
         else:
             torch.mm(a16, w.t(), out=out)
+
+    def _use_own_gemm(self, m: int, n: int, k: int) -> bool:
+        """The tcgen05 kernel takes rows that are whole 16-byte chunks; the choice
+        between it and the library is ``MLS_B200_GEMM`` (tcgen05 | cublas | auto)."""
+        if self.gemm_impl == "cublas" or k % 8 != 0:
+            return False
+        if self.gemm_impl == "tcgen05":
+            return True
+        return m <= 64                      # auto: decoding; prompts go to the library
+
+    def _gemm_bf16(self, a, w, out, m: int, n: int, k: int) -> None:
+        if self._gemm is None:
+            lib = library.load("gemm")
+            self._gemm = _decl(lib, "mls_gemm_bf16",
+                               [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P])
+        swap = 1 if m <= 64 else 0
+        splits, partial = 1, None
+        if swap:
+            # the weights are streamed once: cut K until every SM has a tile
+            # the weights are read once; every tile x split is a CTA, and two CTAs
+            # fit an SM: as many CTAs as fit at the same time, at least 256 of K each
+            tiles = (n + 127) // 128
+            kblocks = (k + 63) // 64
+            splits = max(1, min(kblocks // 4, (2 * 148) // tiles))
+            per = -(-kblocks // splits)
+            splits = -(-kblocks // per)
+            if splits > 1:
+                partial = self.scratch("gemm_partials", splits * m * n)
+        self.launches += 2 if splits > 1 else 1
+        _check(self._gemm(_ptr(a), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                          m, n, k, swap, splits, _ptr(partial), _ptr(self.status),
+                          self._stream()), "gemm_bf16")
 
     def rope_store(self, qkv, positions, cos, sin, slot_map, k_pool, v_pool, n_tokens: int,
                    n_heads: int, n_kv: int, hd: int, max_pos: int, writes: bool) -> None:

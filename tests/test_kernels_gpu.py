@@ -113,16 +113,24 @@ def test_linear_with_float32_weights_in_a_bfloat16_run(rts):
 
 
 @pytest.mark.parametrize("m, n, k", [(1, 128, 64), (8, 6144, 4096), (37, 257, 200), (300, 96, 1000),
-                                     (64, 1000, 4096), (2048, 512, 1024)])
+                                     (64, 1000, 4096), (2048, 512, 1024), (17, 4096, 14336),
+                                     (129, 300, 72), (65, 128, 8), (33, 97, 4096)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_linear_bf16(rts, m, n, k, out_dtype):
+@pytest.mark.parametrize("impl", ["tcgen05", "cublas"])
+def test_linear_bf16(rts, m, n, k, out_dtype, impl):
     ops = rts[torch.bfloat16].ops
     a, w = rand((m, k), torch.bfloat16, 12), rand((n, k), torch.bfloat16, 13, 0.05)
-    out = torch.empty((m, n), dtype=out_dtype, device=DEV)
-    ops.linear(a, ops.prepare_weight(w), out)
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_impl = impl
+    try:
+        ops.linear(a, ops.prepare_weight(w), out)
+    finally:
+        ops.gemm_impl = "auto"
+    ops.check_status()
     want = a.float() @ w.float().t()
     scale = want.abs().max().item()
-    tol = 1e-5 if out_dtype == torch.float32 else 5e-3
+    # float32 sums over k in another order differ by about sqrt(k) roundings
+    tol = max(1e-5, 4 * math.sqrt(k) * 2.0 ** -24) if out_dtype == torch.float32 else 5e-3
     assert (out.float() - want).abs().max().item() <= tol * scale + 1e-6
 
 
