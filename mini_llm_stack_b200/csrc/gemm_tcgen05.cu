@@ -39,7 +39,8 @@ struct GemmParams {
     int ld_out;                          // leading dimension of out (elements)
     int out_f32;                         // 1: out is float32
     int transposed;                      // 1: store D^T (out[n][m])
-    int splits;                          // CTAs along K
+    int splits;                          // parts along K
+    int epilogue;                        // 0: store D; 1: SwiGLU over interleaved gate / up blocks of 16
     int* status;
 };
 
@@ -99,40 +100,116 @@ struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;              // 16 KB
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE = A_BYTES + ((B_BYTES + 1023) / 1024) * 1024;
-    static constexpr int BARS = STAGES * STAGE;              // full[S], empty[S], tmem_full
-    static constexpr int TMEM_SLOT = BARS + 8 * (2 * STAGES + 1);
+    static constexpr int BARS = STAGES * STAGE;              // full[S], empty[S], acc_full[2], acc_empty[2]
+    static constexpr int TMEM_SLOT = BARS + 8 * (2 * STAGES + 4);
     static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;      // + alignment slack
 };
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+// Store 16 consecutive columns (col0 ..) of D's row `row`.  With the SwiGLU
+// epilogue `v` holds 16 gate columns and `u` the 16 matching up columns.
+__device__ __forceinline__ void store_normal(const GemmParams& p, int row, int col0,
+                                             const float (&v)[16], const float (&u)[16]) {
+    if (row >= p.mm) return;
+    float r[16];
+    int col = col0, width = p.nn;
+    if (p.epilogue == 1) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) r[e] = silu_mul(v[e], u[e]);
+        col = col0 >> 1;
+        width = p.nn >> 1;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) r[e] = v[e];
+    }
+    const size_t at = (size_t)row * p.ld_out + col;
+    const bool whole = col + 16 <= width && (p.ld_out % 8) == 0;
+    if (p.out_f32) {
+        float* dst = (float*)p.out + at;
+        if (whole) {
+#pragma unroll
+            for (int e = 0; e < 16; e += 4)
+                *reinterpret_cast<float4*>(dst + e) = make_float4(r[e], r[e + 1], r[e + 2], r[e + 3]);
+        } else {
+            _Pragma("unroll") for (int e = 0; e < 16; ++e) if (col + e < width) dst[e] = r[e];
+        }
+    } else {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + at;
+        if (whole) {
+            uint32_t w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * e], r[2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+            _Pragma("unroll") for (int e = 0; e < 16; ++e) if (col + e < width) dst[e] = __float2bfloat16_rn(r[e]);
+        }
+    }
+}
+
+// The same for the weight-major orientation: D's rows are output features, its
+// columns tokens; out[token][feature].  With the SwiGLU epilogue lanes 0..15 of a
+// warp hold gate features and lanes 16..31 the matching up features.
+__device__ __forceinline__ void store_transposed(const GemmParams& p, int row, int col0,
+                                                 const float (&v)[16], int lane) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const int col = col0 + e;                     // token
+        float val = v[e];
+        int feature = row, width = p.mm;
+        bool mine = true;
+        if (p.epilogue == 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, val, 16);
+            val = silu_mul(val, other);               // meaningful in lanes 0..15
+            feature = ((row - lane) >> 1) + lane;
+            width = p.mm >> 1;
+            mine = lane < 16;
+        }
+        if (col < p.nn && mine && feature < width && row < p.mm) {
+            const size_t at = (size_t)col * p.ld_out + feature;
+            if (p.out_f32) ((float*)p.out)[at] = val;
+            else ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(val);
+        }
+    }
+}
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
                     const __grid_constant__ CUtensorMap bmap) {
     using L = Smem<BN, STAGES>;
-    constexpr int TMEM_COLS = BN < 32 ? 32 : BN;             // a power of two >= 32
-    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && BN % 16 == 0 && BN <= 256, "tile width");
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;     // two accumulators
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && BN % 16 == 0 && TMEM_COLS <= 512,
+                  "tile width");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - raw);
     auto full = [&](int s) { return base + L::BARS + 8u * s; };
     auto empty = [&](int s) { return base + L::BARS + 8u * (STAGES + s); };
-    const uint32_t tmem_full = base + L::BARS + 8u * (2 * STAGES);
+    auto acc_full = [&](int a) { return base + L::BARS + 8u * (2 * STAGES + a); };
+    auto acc_empty = [&](int a) { return base + L::BARS + 8u * (2 * STAGES + 2 + a); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::TMEM_SLOT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int m_tiles = (p.mm + BM - 1) / BM, n_tiles = (p.nn + BN - 1) / BN;
+    const int tile_count = m_tiles * n_tiles * p.splits;
     const int kblocks = (p.k + BK - 1) / BK;
     const int per = (kblocks + p.splits - 1) / p.splits;
-    const int kb0 = blockIdx.z * per, kb1 = min(kblocks, kb0 + per);
-    const int n_kb = max(0, kb1 - kb0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full(s), 1);
             mbar_init(empty(s), 1);
         }
-        mbar_init(tmem_full, 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full(a), 1);
+            mbar_init(acc_empty(a), 4);
+        }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -143,111 +220,125 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_d = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
     bool timed_out = false;
 
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
-                const int slot = i % STAGES;
-                if (!mbar_wait(empty(slot), ((i / STAGES) & 1) ^ 1)) {
-                    timed_out = true;
-                    break;
+            int g = 0;                                       // k-blocks issued so far
+            for (int tile = blockIdx.x; tile < tile_count && !timed_out; tile += gridDim.x) {
+                const int mi = tile % m_tiles, rest = tile / m_tiles;
+                const int ni = rest % n_tiles, z = rest / n_tiles;
+                const int kb0 = z * per, n_kb = max(0, min(kblocks, kb0 + per) - kb0);
+                for (int i = 0; i < n_kb; ++i, ++g) {
+                    const int slot = g % STAGES;
+                    if (!mbar_wait(empty(slot), ((g / STAGES) & 1) ^ 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    const uint32_t a_dst = base + slot * L::STAGE, b_dst = a_dst + L::A_BYTES;
+                    mbar_arrive_expect_tx(full(slot), L::A_BYTES + L::B_BYTES);
+                    tma_load_2d(a_dst, &amap, (kb0 + i) * BK, mi * BM, full(slot));
+                    tma_load_2d(b_dst, &bmap, (kb0 + i) * BK, ni * BN, full(slot));
                 }
-                const uint32_t a_dst = base + slot * L::STAGE, b_dst = a_dst + L::A_BYTES;
-                mbar_arrive_expect_tx(full(slot), L::A_BYTES + L::B_BYTES);
-                tma_load_2d(a_dst, &amap, (kb0 + i) * BK, m0, full(slot));
-                tma_load_2d(b_dst, &bmap, (kb0 + i) * BK, n0, full(slot));
             }
         }
     } else if (warp == 1) {
         // --------------------------------------------------------------- MMA issue
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BN);
-            for (int i = 0; i < n_kb; ++i) {
-                const int slot = i % STAGES;
-                if (!mbar_wait(full(slot), (i / STAGES) & 1)) {
+            int g = 0, it = 0;
+            for (int tile = blockIdx.x; tile < tile_count && !timed_out; tile += gridDim.x, ++it) {
+                const int z = tile / (m_tiles * n_tiles);
+                const int kb0 = z * per, n_kb = max(0, min(kblocks, kb0 + per) - kb0);
+                const int acc = it & 1;
+                if (!mbar_wait(acc_empty(acc), ((it >> 1) & 1) ^ 1)) {
                     timed_out = true;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t a_src = base + slot * L::STAGE, b_src = a_src + L::A_BYTES;
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int i = 0; i < n_kb; ++i, ++g) {
+                    const int slot = g % STAGES;
+                    if (!mbar_wait(full(slot), (g / STAGES) & 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_src = base + slot * L::STAGE, b_src = a_src + L::A_BYTES;
 #pragma unroll
-                for (int kk = 0; kk < BK / UMMA_K; ++kk)
-                    umma(tmem_d, umma_desc(a_src + kk * UMMA_K * 2),
-                         umma_desc(b_src + kk * UMMA_K * 2), idesc, (i | kk) ? 1u : 0u);
-                umma_commit(empty(slot));           // the stage is free when these are done
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                        umma(tmem_d, umma_desc(a_src + kk * UMMA_K * 2),
+                             umma_desc(b_src + kk * UMMA_K * 2), idesc, (i | kk) ? 1u : 0u);
+                    umma_commit(empty(slot));       // the stage is free when these are done
+                }
+                umma_commit(acc_full(acc));         // the accumulator is complete
             }
-            umma_commit(tmem_full);                 // the accumulator is complete
         }
     } else {
         // ---------------------------------------------------------------- epilogue
-        if (n_kb > 0 && !mbar_wait(tmem_full, 0)) timed_out = true;
-        tc_fence_after();
         const int q = warp & 3;                     // this warp's quarter of the 128 lanes
-        const int row = m0 + q * 32 + lane;         // row of A (and of D)
-        const bool to_partial = p.splits > 1;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-            uint32_t v[16];
-            if (n_kb > 0) {
-                tmem_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + c0, v);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int e = 0; e < 16; ++e) v[e] = 0u;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tile_count; tile += gridDim.x, ++it) {
+            const int mi = tile % m_tiles, rest = tile / m_tiles;
+            const int ni = rest % n_tiles, z = rest / n_tiles;
+            const int acc = it & 1;
+            const int row = mi * BM + q * 32 + lane;
+            if (!mbar_wait(acc_full(acc), (it >> 1) & 1)) {
+                timed_out = true;
+                break;
             }
-            if (row >= p.mm) continue;
-            if (p.transposed) {
-                // out[col][row]: the 32 lanes of a warp write 32 consecutive rows
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+            const bool to_partial = p.splits > 1;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t ra[16], rb[16];
+                tmem_ld16(tmem_d + c0, ra);
+                if (BN > 16) tmem_ld16(tmem_d + c0 + 16, rb);
+                tmem_ld_wait();
+                float va[16], vb[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    const int col = n0 + c0 + e;
-                    if (col >= p.nn) break;
-                    const size_t at = (size_t)col * p.ld_out + row;
-                    const float f = __uint_as_float(v[e]);
-                    if (to_partial)
-                        p.partial[(size_t)blockIdx.z * p.nn * p.ld_out + at] = f;
-                    else if (p.out_f32)
-                        ((float*)p.out)[at] = f;
-                    else
-                        ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(f);
+                    va[e] = __uint_as_float(ra[e]);
+                    vb[e] = BN > 16 ? __uint_as_float(rb[e]) : 0.f;
                 }
-            } else {
-                const int col = n0 + c0;
-                const size_t at = (size_t)row * p.ld_out + col;
-                const bool whole = col + 16 <= p.nn && (p.ld_out % 8) == 0;
+                const int col = ni * BN + c0;
                 if (to_partial) {
-                    float* dst = p.partial + (size_t)blockIdx.z * p.mm * p.ld_out + at;
-                    for (int e = 0; e < 16 && col + e < p.nn; ++e) dst[e] = __uint_as_float(v[e]);
-                } else if (p.out_f32) {
-                    float* dst = (float*)p.out + at;
-                    if (whole) {
+                    if (row < p.mm) {
+                        if (p.transposed) {
+                            // [part][token][feature]: a warp writes 32 consecutive features
+                            float* dst = p.partial + ((size_t)z * p.nn + col) * p.mm + row;
 #pragma unroll
-                        for (int e = 0; e < 16; e += 4)
-                            *reinterpret_cast<uint4*>(dst + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-                    } else {
-                        for (int e = 0; e < 16 && col + e < p.nn; ++e) dst[e] = __uint_as_float(v[e]);
-                    }
-                } else {
-                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + at;
-                    if (whole) {
-                        uint32_t w[8];
+                            for (int e = 0; e < 16; ++e) {
+                                if (col + e < p.nn) dst[(size_t)e * p.mm] = va[e];
+                                if (BN > 16 && col + 16 + e < p.nn) dst[(size_t)(16 + e) * p.mm] = vb[e];
+                            }
+                        } else {
+                            float* dst = p.partial + ((size_t)z * p.mm + row) * p.nn + col;
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * e]),
-                                                                     __uint_as_float(v[2 * e + 1]));
-                            w[e] = *reinterpret_cast<uint32_t*>(&h);
+                            for (int e = 0; e < 16; ++e) {
+                                if (col + e < p.nn) dst[e] = va[e];
+                                if (BN > 16 && col + 16 + e < p.nn) dst[16 + e] = vb[e];
+                            }
                         }
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-                        *reinterpret_cast<uint4*>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-                    } else {
-                        for (int e = 0; e < 16 && col + e < p.nn; ++e)
-                            dst[e] = __float2bfloat16_rn(__uint_as_float(v[e]));
                     }
+                } else if (p.transposed) {
+                    store_transposed(p, row, col, va, lane);
+                    if (BN > 16) store_transposed(p, row, col + 16, vb, lane);
+                } else if (p.epilogue == 1) {
+                    store_normal(p, row, col, va, vb);
+                } else {
+                    store_normal(p, row, col, va, va);
+                    if (BN > 16) store_normal(p, row, col + 16, vb, vb);
                 }
             }
+            // the accumulator has been read: the MMA warp may fill it again
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(acc));
+
         }
     }
     if (timed_out && p.status) atomicOr(p.status, MLS_STATUS_TIMEOUT);
@@ -255,19 +346,36 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
-                     ::"r"(tmem_d), "r"(TMEM_COLS) : "memory");
+                     ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
-// sum of split-K partial results: out[i] = sum_s partial[s][i]
+// Sum of the split-K parts, then the epilogue.  Parts are [part][row][col] in the
+// order the output has ([token][feature] in both orientations).
 __global__ void splitk_sum_kernel(const float* __restrict__ partial, void* __restrict__ out,
-                                  int out_f32, size_t n, int splits) {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+                                  int out_f32, int rows, int cols, int splits, int epilogue) {
+    const size_t n = (size_t)rows * cols;
+    const int out_cols = epilogue == 1 ? cols / 2 : cols;
+    const size_t total = (size_t)rows * out_cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
-        float s = 0.f;
-        for (int k = 0; k < splits; ++k) s += partial[(size_t)k * n + i];
-        if (out_f32) ((float*)out)[i] = s;
-        else ((__nv_bfloat16*)out)[i] = __float2bfloat16_rn(s);
+        float r;
+        if (epilogue == 1) {
+            const size_t row = i / out_cols;
+            const int f = (int)(i - row * out_cols);
+            const size_t g = row * cols + (size_t)(f / 16) * 32 + (f % 16);
+            float gs = 0.f, us = 0.f;
+            for (int k = 0; k < splits; ++k) {
+                gs += partial[(size_t)k * n + g];
+                us += partial[(size_t)k * n + g + 16];
+            }
+            r = silu_mul(gs, us);
+        } else {
+            r = 0.f;
+            for (int k = 0; k < splits; ++k) r += partial[(size_t)k * n + i];
+        }
+        if (out_f32) ((float*)out)[i] = r;
+        else ((__nv_bfloat16*)out)[i] = __float2bfloat16_rn(r);
     }
 }
 
@@ -298,7 +406,8 @@ bool operand_map(const void* ptr, long long rows, long long k, int box_rows, CUt
 }
 
 template <int BN, int STAGES>
-int launch(const GemmParams& p, const void* a, const void* b, cudaStream_t stream) {
+int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
+           cudaStream_t stream) {
     using L = Smem<BN, STAGES>;
     static bool configured = false;
     if (!configured) {
@@ -310,52 +419,56 @@ int launch(const GemmParams& p, const void* a, const void* b, cudaStream_t strea
     CUtensorMap amap, bmap;
     if (!operand_map(a, p.mm, p.k, BM, &amap) || !operand_map(b, p.nn, p.k, BN, &bmap))
         return MLS_ERR_TENSOR_MAP;
-    dim3 grid((p.mm + BM - 1) / BM, (p.nn + BN - 1) / BN, p.splits);
+    const long long tiles = (long long)((p.mm + BM - 1) / BM) * ((p.nn + BN - 1) / BN) * p.splits;
+    const long long most = 148LL * ctas_per_sm;
+    const int grid = (int)(tiles < most ? tiles : most);
     gemm_tcgen05_kernel<BN, STAGES><<<grid, THREADS, L::TOTAL, stream>>>(p, amap, bmap);
     return launch_status();
 }
 }  // namespace
 
 // out[M, N] = act[M, K] * w[N, K]^T, bfloat16 operands, out bfloat16 or float32.
-// swap: 1 = the weights take the 128-row side (decoding, M <= 64); splits > 1 cuts K
-// and needs `partial`, float32 scratch of splits * M * N.
+// swap: 1 = the weights take the 128-row side (decoding, M <= 64).  splits > 1 cuts K
+// (weight-major orientation only) and needs `partial`, float32 scratch of
+// splits * M * N, which a second kernel adds up.  epilogue 1: the weight rows alternate between
+// 16 gate rows and the 16 matching up rows, and out[M, N / 2] = silu(gate) * up.
 MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32, int m, int n,
-                          int k, int swap, int splits, float* partial, int* status,
+                          int k, int swap, int splits, int epilogue, float* partial, int* status,
                           cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k % 8 != 0 || k <= 0) return MLS_ERR_UNSUPPORTED;      // rows must be 16-byte multiples
-    if (splits < 1 || (splits > 1 && partial == nullptr)) return MLS_ERR_UNSUPPORTED;
+    if (splits < 1 || (splits > 1 && partial == nullptr))
+        return MLS_ERR_UNSUPPORTED;
+    if (epilogue == 1 && n % 32 != 0) return MLS_ERR_UNSUPPORTED;
     GemmParams p;
     p.out = out;
     p.partial = partial;
     p.k = k;
-    p.ld_out = n;
+    p.ld_out = epilogue == 1 ? n / 2 : n;
     p.out_f32 = out_f32;
     p.splits = splits;
+    p.epilogue = epilogue;
     p.status = status;
-    int rc;
     if (swap) {
         if (m > 64) return MLS_ERR_UNSUPPORTED;
         p.mm = n;                       // rows of the weights
         p.nn = m;                       // tokens
         p.transposed = 1;
         // two CTAs fit an SM, so up to 296 tiles stream at the same time
-        if (m <= 16) rc = launch<16, 6>(p, w, act, stream);
-        else if (m <= 32) rc = launch<32, 5>(p, w, act, stream);
-        else rc = launch<64, 4>(p, w, act, stream);
-    } else {
-        p.mm = m;
-        p.nn = n;
-        p.transposed = 0;
-        rc = launch<256, 4>(p, act, w, stream);
-    }
-    if (rc) return rc;
-    if (splits > 1) {
-        const size_t total = (size_t)m * n;
+        int rc;
+        if (m <= 16) rc = launch<16, 6>(p, w, act, 2, stream);
+        else if (m <= 32) rc = launch<32, 5>(p, w, act, 2, stream);
+        else rc = launch<64, 4>(p, w, act, 2, stream);
+        if (rc || splits == 1) return rc;
+        const size_t total = (size_t)m * p.ld_out;
         int blocks = (int)((total + 255) / 256);
         if (blocks > 148 * 8) blocks = 148 * 8;
-        splitk_sum_kernel<<<blocks, 256, 0, stream>>>(partial, out, out_f32, total, splits);
+        splitk_sum_kernel<<<blocks, 256, 0, stream>>>(partial, out, out_f32, m, n, splits, epilogue);
         return launch_status();
     }
-    return 0;
+    if (splits != 1) return MLS_ERR_UNSUPPORTED;               // prompts have tiles enough
+    p.mm = m;
+    p.nn = n;
+    p.transposed = 0;
+    return launch<256, 4>(p, act, w, 1, stream);
 }

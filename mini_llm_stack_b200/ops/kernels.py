@@ -197,19 +197,18 @@ class Ops:
         between it and the library is ``MLS_B200_GEMM`` (tcgen05 | cublas | auto)."""
         if self.gemm_impl == "cublas" or k % 8 != 0:
             return False
-        if self.gemm_impl == "tcgen05":
-            return True
-        return m <= 64                      # auto: decoding; prompts go to the library
+        # auto: plain products go to the library (as the reference's nn.Linear does);
+        # the tcgen05 kernel runs where it fuses work (``linear_swiglu``)
+        return self.gemm_impl == "tcgen05"
 
-    def _gemm_bf16(self, a, w, out, m: int, n: int, k: int) -> None:
+    def _gemm_bf16(self, a, w, out, m: int, n: int, k: int, epilogue: int = 0) -> None:
         if self._gemm is None:
             lib = library.load("gemm")
             self._gemm = _decl(lib, "mls_gemm_bf16",
-                               [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P])
+                               [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P])
         swap = 1 if m <= 64 else 0
         splits, partial = 1, None
         if swap:
-            # the weights are streamed once: cut K until every SM has a tile
             # the weights are read once; every tile x split is a CTA, and two CTAs
             # fit an SM: as many CTAs as fit at the same time, at least 256 of K each
             tiles = (n + 127) // 128
@@ -221,8 +220,33 @@ class Ops:
                 partial = self.scratch("gemm_partials", splits * m * n)
         self.launches += 2 if splits > 1 else 1
         _check(self._gemm(_ptr(a), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
-                          m, n, k, swap, splits, _ptr(partial), _ptr(self.status),
+                          m, n, k, swap, splits, epilogue, _ptr(partial), _ptr(self.status),
                           self._stream()), "gemm_bf16")
+
+    def can_fuse_swiglu(self, d_model: int, inter: int) -> bool:
+        """Whether gate-up projection and SwiGLU can run as one kernel."""
+        return (self.act_dtype == torch.bfloat16 and self.gemm_impl != "cublas"
+                and inter % 16 == 0 and d_model % 8 == 0)
+
+    @staticmethod
+    def interleave_gate_up(w_gate, w_up):
+        """Rows [16 gate | 16 up | 16 gate | ...]: the layout ``linear_swiglu`` reads."""
+        i, d = w_gate.shape
+        both = torch.stack([w_gate.view(i // 16, 16, d), w_up.view(i // 16, 16, d)], dim=1)
+        return both.reshape(2 * i, d).contiguous()
+
+    def linear_swiglu(self, a, w_interleaved, out) -> None:
+        """``out[M, I] = silu(a @ Wg^T) * (a @ Wu^T)`` in one kernel; the weight holds
+        gate and up rows interleaved in blocks of 16 (``interleave_gate_up``)."""
+        m, k = a.shape
+        n = w_interleaved.shape[0]
+        _need(out.shape == (m, n // 2) and a.dtype == torch.bfloat16 and
+              w_interleaved.dtype == torch.bfloat16, "linear_swiglu: shapes or types do not fit")
+        _need(a.is_contiguous() and w_interleaved.is_contiguous() and out.is_contiguous(),
+              "linear_swiglu: operands must be contiguous")
+        if m == 0:
+            return
+        self._gemm_bf16(a, w_interleaved, out, m, n, k, epilogue=1)
 
     def rope_store(self, qkv, positions, cos, sin, slot_map, k_pool, v_pool, n_tokens: int,
                    n_heads: int, n_kv: int, hd: int, max_pos: int, writes: bool) -> None:

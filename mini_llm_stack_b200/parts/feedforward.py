@@ -2,7 +2,8 @@
 
 Reference (train/model.py:127-135): ``w_down(silu(w_gate x) * (w_up x))`` with
 ``silu(z) = z * sigmoid(z)``, no biases.  Gate and up share one projection
-here (rows [gate | up]); ``silu(gate) * up`` is computed in float32.
+here; ``silu(gate) * up`` is computed in float32, in the projection's own
+epilogue where the tcgen05 kernel takes the sizes.
 """
 
 from __future__ import annotations
@@ -30,17 +31,28 @@ class SwiGLUFeedForward(FeedForward):
         parts = [tensors["w_gate.weight"], tensors["w_up.weight"]]
         if parts[0].dtype != parts[1].dtype:
             parts = [p.float() for p in parts]
-        self.w_gate_up = runtime.ops.prepare_weight(torch.cat(parts, dim=0))
-        self.w_down = runtime.ops.prepare_weight(tensors["w_down.weight"])
+        ops = runtime.ops
+        # one kernel for projection and activation where the tensor-core kernel takes
+        # the sizes: its weight holds gate and up rows interleaved in blocks of 16
+        self.fused = (parts[0].dtype == torch.bfloat16
+                      and ops.can_fuse_swiglu(self.d_model, self.intermediate_size))
+        if self.fused:
+            self.w_gate_up = ops.prepare_weight(ops.interleave_gate_up(parts[0], parts[1]))
+        else:
+            self.w_gate_up = ops.prepare_weight(torch.cat(parts, dim=0))
+        self.w_down = ops.prepare_weight(tensors["w_down.weight"])
 
     def forward(self, h, step: StepContext):
         rt = self.runtime
         t = h.shape[0]
         i = self.intermediate_size
-        gu = rt.buffer("gate_up", (t, 2 * i), rt.act_dtype)
-        rt.ops.linear(h, self.w_gate_up, gu)
         act = rt.buffer("ffn_act", (t, i), rt.act_dtype)
-        rt.ops.swiglu(gu, act)
+        if self.fused:
+            rt.ops.linear_swiglu(h, self.w_gate_up, act)
+        else:
+            gu = rt.buffer("gate_up", (t, 2 * i), rt.act_dtype)
+            rt.ops.linear(h, self.w_gate_up, gu)
+            rt.ops.swiglu(gu, act)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
         rt.ops.linear(act, self.w_down, delta)
         return delta

@@ -134,6 +134,22 @@ def test_linear_bf16(rts, m, n, k, out_dtype, impl):
     assert (out.float() - want).abs().max().item() <= tol * scale + 1e-6
 
 
+@pytest.mark.parametrize("m, inter, k", [(1, 14336, 4096), (8, 176, 64), (64, 256, 96), (33, 4096, 4096),
+                                          (300, 272, 200), (2048, 1024, 512), (129, 14336, 1024)])
+def test_gate_up_projection_with_swiglu_epilogue(rts, m, inter, k):
+    ops = rts[torch.bfloat16].ops
+    a = rand((m, k), torch.bfloat16, 30)
+    wg, wu = rand((inter, k), torch.bfloat16, 31, 0.08), rand((inter, k), torch.bfloat16, 32, 0.08)
+    assert ops.can_fuse_swiglu(k, inter)
+    out = torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(a, ops.interleave_gate_up(wg, wu), out)
+    ops.check_status()
+    g = (a.float() @ wg.float().t()).cpu()
+    u = (a.float() @ wu.float().t()).cpu()
+    want = torch.nn.functional.silu(g) * u
+    assert (out.float().cpu() - want).abs().max().item() <= 8e-3 * want.abs().max().item() + 1e-6
+
+
 # ------------------------------------------------------------------------- swiglu
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("t, inter", [(3, 172), (17, 14336), (1, 5)])
