@@ -1,0 +1,451 @@
+// Causal grouped-query attention for prompts and portions on the 5th-generation
+// tensor cores (tcgen05), compiled for one head size (64 or 128).
+//
+// Reference math (train/model.py:55-70): S = (q . k) * scale, key j hidden from the
+// query at position p iff j > p (or j <= p - window); softmax and P . V with float32
+// scores, maxima, sums and accumulators; P rounded to bfloat16 for the second
+// product (kernels/attention_fwd.py:106).
+//
+// One CTA owns 128 rows, (token, head-in-group) pairs of one kv head, and walks the
+// keys 128 at a time:
+//   warp 0      brings keys and values in with TMA, one copy per page and 64-wide half;
+//   warp 1      issues S = Q K^T and O += P V (tcgen05.mma), accumulators in TMEM;
+//   warps 2..5  one thread per row: read S from TMEM, scale, mask, exponentiate, write P
+//               to shared memory as the next product's operand, rescale O when the
+//               running maximum has grown by more than 2^8, and store O at the end.
+// S is double-buffered in TMEM so that the next tile's Q K^T runs during the softmax.
+// Every wait is bounded and reports MLS_STATUS_TIMEOUT.
+#include "common.cuh"
+#include "tma.cuh"
+#include "tcgen05.cuh"
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#ifndef MLS_HEAD_DIM
+#error "compile with -DMLS_HEAD_DIM=<head size>"
+#endif
+
+#if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
+namespace {
+using namespace mls_tma;
+using namespace mls_tc;
+
+constexpr int HD = MLS_HEAD_DIM;
+constexpr int ROWS = 128;                        // rows of a tile
+constexpr int BN = 128;                          // keys of a tile
+constexpr int HALVES = HD / 64;
+constexpr int BLOCK = 128 * 128;                 // bytes of [128 rows][64 elements]: 16 KB
+constexpr int Q_BYTES = HALVES * BLOCK;
+constexpr int P_BYTES = 2 * BLOCK;               // 128 keys = two 64-wide K blocks
+constexpr int KV_STAGE = 2 * HALVES * BLOCK;     // keys, then values
+constexpr int STAGES = 2;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;                   // S0 | S1 | O
+constexpr int COL_S = 0, COL_O = 2 * BN;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.0f;             // log2: P stays below 2^8
+
+// barrier slots
+constexpr int B_KV_FULL = 0, B_KV_EMPTY = 2, B_S_FULL = 4, B_S_EMPTY = 6, B_P_FULL = 8,
+              B_P_EMPTY = 9, B_Q_FULL = 10, N_BARS = 11;
+constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + STAGES * KV_STAGE + 8 * N_BARS + 16 + 1024;
+
+struct Params {
+    const __nv_bfloat16* qkv;
+    __nv_bfloat16* out;
+    const int* block_table;
+    const int* cu_q;
+    const int* ctx_len;
+    int max_blocks, n_req, n_heads, n_kv, group, block_size, window, small_only;
+    float scale_log2;
+    int* status;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ bool is_small(int q_len, int group) { return q_len * group <= 16; }
+
+// address of the 16-byte chunk `chunk` of row `row` in a [..][128 rows][64] block set
+__device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
+    return tile + (chunk >> 3) * BLOCK + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(THREADS)
+attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
+                    const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - raw);
+    const uint32_t q_smem = base, p_smem = base + Q_BYTES, kv_smem = p_smem + P_BYTES;
+    const uint32_t bars = kv_smem + STAGES * KV_STAGE;
+    auto bar = [&](int i) { return bars + 8u * i; };
+    volatile uint32_t* tmem_slot =
+        reinterpret_cast<volatile uint32_t*>(gbase + (bars - base) + 8 * N_BARS);
+
+    // which request and which 128-row tile of it; the last rows see the most keys
+    int r = 0, tile = blockIdx.x, q_len = 0, rows = 0;
+    for (; r < P.n_req; ++r) {
+        q_len = P.cu_q[r + 1] - P.cu_q[r];
+        rows = q_len * P.group;
+        int tiles = (P.small_only && is_small(q_len, P.group)) ? 0 : (rows + ROWS - 1) / ROWS;
+        if (tile < tiles) break;
+        tile -= tiles;
+    }
+    if (r >= P.n_req) return;
+    tile = (rows + ROWS - 1) / ROWS - 1 - tile;
+    const int kvh = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
+    const int row0 = tile * ROWS;
+    const int pos0 = ctx - q_len;
+    const int i_first = row0 / P.group;
+    const int i_last = (min(rows, row0 + ROWS) - 1) / P.group;
+    const int hi = pos0 + i_last;
+    const int lo = P.window > 0 ? max(0, pos0 + i_first - P.window + 1) : 0;
+    const int* table = P.block_table + (size_t)r * P.max_blocks;
+    const int kbase0 = (lo / BN) * BN;
+    const int n_tiles = (hi - kbase0) / BN + 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar(B_KV_FULL + s), 1);
+            mbar_init(bar(B_KV_EMPTY + s), 1);
+            mbar_init(bar(B_S_FULL + s), 1);
+            mbar_init(bar(B_S_EMPTY + s), 128);
+        }
+        mbar_init(bar(B_P_FULL), 128);
+        mbar_init(bar(B_P_EMPTY), 1);
+        mbar_init(bar(B_Q_FULL), 128);
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool timed_out = false;
+
+    if (warp == 0) {
+        // -------------------------------------------------------------- TMA producer
+        const int bs = P.block_size, ppt = BN / bs;
+        const uint32_t page_bytes = bs * 128;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int slot = t % STAGES;
+            if (!mbar_wait(bar(B_KV_EMPTY + slot), ((t / STAGES) & 1) ^ 1)) {
+                timed_out = true;
+                break;
+            }
+            const int kb = kbase0 + t * BN;
+            const uint32_t stage = kv_smem + slot * KV_STAGE;
+            bool valid = false;
+            int page = -1;
+            if (lane < ppt) {
+                const int j0 = kb + lane * bs;
+                if (j0 <= hi && j0 + bs > lo) {
+                    page = table[j0 / bs];
+                    valid = page >= 0;
+                }
+            }
+            const unsigned mask = __ballot_sync(0xffffffffu, valid);
+            const unsigned all = ppt >= 32 ? 0xffffffffu : ((1u << ppt) - 1u);
+            if (mask != all) {
+                // pages that are not keys of this request read as zeros
+                for (int pi = 0; pi < ppt; ++pi) {
+                    if ((mask >> pi) & 1u) continue;
+                    for (int part = 0; part < 2 * HALVES; ++part) {
+                        const uint32_t dst = stage + part * BLOCK + pi * page_bytes;
+                        for (uint32_t o = lane * 16; o < page_bytes; o += 512)
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(dst + o),
+                                         "r"(0u) : "memory");
+                    }
+                }
+                fence_proxy_async();
+            }
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_expect_tx(bar(B_KV_FULL + slot), __popc(mask) * page_bytes * 2 * HALVES);
+            __syncwarp();
+            if (valid) {
+                const int y = (page * P.n_kv + kvh) * bs;
+#pragma unroll
+                for (int h = 0; h < HALVES; ++h) {
+                    tma_load_2d(stage + h * BLOCK + lane * page_bytes, &kmap, h * 64, y,
+                                bar(B_KV_FULL + slot));
+                    tma_load_2d(stage + (HALVES + h) * BLOCK + lane * page_bytes, &vmap, h * 64, y,
+                                bar(B_KV_FULL + slot));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issue
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc(BN, 0);
+            constexpr uint32_t idesc_o = umma_idesc(HD, 1);
+            auto issue_qk = [&](int j) -> bool {
+                const int slot = j % STAGES, sb = j & 1;
+                if (!mbar_wait(bar(B_KV_FULL + slot), (j / STAGES) & 1)) return false;
+                if (!mbar_wait(bar(B_S_EMPTY + sb), ((j >> 1) & 1) ^ 1)) return false;
+                tc_fence_after();
+                const uint32_t k_src = kv_smem + slot * KV_STAGE;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * BLOCK + (kk & 3) * 32;
+                    umma(tmem + COL_S + sb * BN, umma_desc(q_smem + off), umma_desc(k_src + off),
+                         idesc_s, kk ? 1u : 0u);
+                }
+                umma_commit(bar(B_S_FULL + sb));
+                return true;
+            };
+            if (!mbar_wait(bar(B_Q_FULL), 0)) timed_out = true;
+            if (!timed_out && n_tiles > 0 && !issue_qk(0)) timed_out = true;
+            for (int j = 0; j < n_tiles && !timed_out; ++j) {
+                if (j + 1 < n_tiles && !issue_qk(j + 1)) {
+                    timed_out = true;
+                    break;
+                }
+                if (!mbar_wait(bar(B_P_FULL), j & 1)) {
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t v_src = kv_smem + (j % STAGES) * KV_STAGE + HALVES * BLOCK;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t p_off = (kk >> 2) * BLOCK + (kk & 3) * 32;
+                    umma(tmem + COL_O, umma_desc(p_smem + p_off),
+                         umma_desc_mn(v_src + kk * 16 * 128, BLOCK), idesc_o, (j | kk) ? 1u : 0u);
+                }
+                umma_commit(bar(B_KV_EMPTY + (j % STAGES)));   // keys and values of tile j are done with
+                umma_commit(bar(B_P_EMPTY));                   // P is free, O holds tile j
+            }
+        }
+    } else {
+        // ------------------------------------------------- softmax, correction, epilogue
+        const int q = warp & 3;
+        const int row_in = q * 32 + lane;                      // row of the tile = TMEM lane
+        const int row = row0 + row_in;
+        const bool live = row < rows;
+        const int ti = live ? row / P.group : 0, g = live ? row - ti * P.group : 0;
+        const int pos = live ? pos0 + ti : -1;
+        const int lo_row = P.window > 0 ? pos - P.window + 1 : 0;
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+
+        // this thread's row of Q into shared memory, in the operand layout
+        {
+            const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
+            const __nv_bfloat16* src =
+                P.qkv + (size_t)(tok0 + ti) * row_w + (size_t)(kvh * P.group + g) * HD;
+#pragma unroll
+            for (int c = 0; c < HD / 8; ++c) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (live) v = *reinterpret_cast<const uint4*>(src + c * 8);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(swz(q_smem, row_in, c)),
+                             "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            }
+            fence_proxy_async();
+            mbar_arrive(bar(B_Q_FULL));
+        }
+
+        float m_used = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_tiles && !timed_out; ++j) {
+            const int sb = j & 1;
+            const int kbase = kbase0 + j * BN;
+            if (!mbar_wait(bar(B_S_FULL + sb), (j >> 1) & 1)) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t s_addr = tmem + lane_base + COL_S + sb * BN;
+            // pass 1: the row's maximum over this tile
+            float m_tile = -INFINITY;
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t a[16], b[16];
+                tmem_ld16(s_addr + c0, a);
+                tmem_ld16(s_addr + c0 + 16, b);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const int ja = kbase + c0 + e, jb = ja + 16;
+                    if (ja <= pos && ja >= lo_row)
+                        m_tile = fmaxf(m_tile, __uint_as_float(a[e]) * P.scale_log2);
+                    if (jb <= pos && jb >= lo_row)
+                        m_tile = fmaxf(m_tile, __uint_as_float(b[e]) * P.scale_log2);
+                }
+            }
+            // P of the previous tile must have been consumed, and O must be at rest
+            if (j > 0 && !mbar_wait(bar(B_P_EMPTY), (j - 1) & 1)) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const bool grow = m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > m_used);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? m_tile : m_used;
+                const float c = (grow && m_used != -INFINITY) ? fast_exp2(m_used - m_new) : 1.0f;
+                if (j > 0) {
+                    const uint32_t o_addr = tmem + lane_base + COL_O;
+#pragma unroll
+                    for (int c0 = 0; c0 < HD; c0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(o_addr + c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * c);
+                        tmem_st16(o_addr + c0, v);
+                    }
+                    tmem_st_wait();
+                }
+                l *= c;
+                m_used = m_new;
+            }
+            // pass 2: probabilities, their sum, and P as the next product's operand
+            const float base_m = m_used == -INFINITY ? 0.f : m_used;
+            float sum = 0.f;
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t a[16], b[16];
+                tmem_ld16(s_addr + c0, a);
+                tmem_ld16(s_addr + c0 + 16, b);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 16; e += 2) {
+                    float p[4];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int ja = kbase + c0 + e + u, jb = ja + 16;
+                        p[u] = (ja <= pos && ja >= lo_row)
+                                   ? fast_exp2(__uint_as_float(a[e + u]) * P.scale_log2 - base_m) : 0.f;
+                        p[2 + u] = (jb <= pos && jb >= lo_row)
+                                       ? fast_exp2(__uint_as_float(b[e + u]) * P.scale_log2 - base_m) : 0.f;
+                    }
+                    sum += (p[0] + p[1]) + (p[2] + p[3]);
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0], p[1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(p[2], p[3]);
+                    pk[e >> 1] = *reinterpret_cast<uint32_t*>(&h0);
+                    pk[8 + (e >> 1)] = *reinterpret_cast<uint32_t*>(&h1);
+                }
+                // keys c0 .. c0+31 of this row: four 16-byte chunks
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch)
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
+                                 ::"r"(swz(p_smem, row_in, (c0 >> 3) + ch)), "r"(pk[4 * ch]),
+                                   "r"(pk[4 * ch + 1]), "r"(pk[4 * ch + 2]), "r"(pk[4 * ch + 3])
+                                 : "memory");
+            }
+            l += sum;
+            tc_fence_before();
+            fence_proxy_async();
+            mbar_arrive(bar(B_S_EMPTY + sb));
+            mbar_arrive(bar(B_P_FULL));
+        }
+        // the last P V, then the row's output
+        if (!timed_out && n_tiles > 0 && !mbar_wait(bar(B_P_EMPTY), (n_tiles - 1) & 1))
+            timed_out = true;
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
+                             (size_t)(kvh * P.group + g) * HD;
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 16) {
+            uint32_t v[16];
+            tmem_ld16(tmem + lane_base + COL_O + c0, v);
+            tmem_ld_wait();
+            if (live) {
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * e]) * inv,
+                                                             __uint_as_float(v[2 * e + 1]) * inv);
+                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+        }
+    }
+    if (timed_out && (threadIdx.x & 31) == 0 && P.status) atomicOr(P.status, MLS_STATUS_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+struct MapKey {
+    const void* ptr;
+    long long rows;
+    int block;
+    bool operator<(const MapKey& o) const {
+        return std::tie(ptr, rows, block) < std::tie(o.ptr, o.rows, o.block);
+    }
+};
+std::map<MapKey, CUtensorMap> g_maps;
+std::mutex g_lock;
+
+bool pool_map(const void* pool, long long pool_rows, int block, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    MapKey key{pool, pool_rows, block};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        CUtensorMap m;
+        if (!make_map_bf16_2d(&m, pool, HD, (uint64_t)pool_rows, (uint64_t)HD * 2, 64, block))
+            return false;
+        it = g_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return true;
+}
+}  // namespace
+#endif
+
+// Prompts and portions of a step: n_tiles = number of 128-row tiles (requests that
+// the split kernel takes are left out when skip_small is set).  Returns
+// MLS_ERR_UNSUPPORTED (and launches nothing) for head or page sizes it does not take.
+MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, const void* v_pool,
+                             const int* block_table, int max_blocks, const int* cu_q,
+                             const int* ctx_len, int n_req, int n_heads, int n_kv, int block_size,
+                             float scale, int window, int n_tiles, int skip_small,
+                             long long pool_pages, int* status, cudaStream_t stream) {
+#if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
+    if (n_tiles <= 0 || n_req <= 0) return 0;
+    if (n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
+    if (!(block_size == 8 || block_size == 16 || block_size == 32 || block_size == 64))
+        return MLS_ERR_UNSUPPORTED;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap kmap, vmap;
+    const long long rows = pool_pages * n_kv * block_size;
+    if (!pool_map(k_pool, rows, block_size, &kmap) || !pool_map(v_pool, rows, block_size, &vmap))
+        return MLS_ERR_TENSOR_MAP;
+    Params P;
+    P.qkv = (const __nv_bfloat16*)qkv;
+    P.out = (__nv_bfloat16*)out;
+    P.block_table = block_table;
+    P.cu_q = cu_q;
+    P.ctx_len = ctx_len;
+    P.max_blocks = max_blocks;
+    P.n_req = n_req;
+    P.n_heads = n_heads;
+    P.n_kv = n_kv;
+    P.group = n_heads / n_kv;
+    P.block_size = block_size;
+    P.window = window;
+    P.small_only = skip_small ? 1 : 0;
+    P.scale_log2 = scale * LOG2E;
+    P.status = status;
+    attention_tc_kernel<<<dim3(n_tiles, n_kv), THREADS, SMEM_BYTES, stream>>>(P, kmap, vmap);
+    return launch_status();
+#else
+    return MLS_ERR_UNSUPPORTED;
+#endif
+}

@@ -20,14 +20,16 @@
 // kernel still frees its tensor memory and returns.
 #include "common.cuh"
 #include "tma.cuh"
+#include "tcgen05.cuh"
 #include <map>
 #include <mutex>
 #include <tuple>
 
 namespace {
 using namespace mls_tma;
+using namespace mls_tc;
 
-constexpr int BM = 128;                  // rows of A per tile = UMMA M
+constexpr int BM = mls_tc::UMMA_M;       // rows of A per tile
 constexpr int BK = 64;                   // K elements per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
@@ -43,57 +45,6 @@ struct GemmParams {
     int epilogue;                        // 0: store D; 1: SwiGLU over interleaved gate / up blocks of 16
     int* status;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-// Shared-memory matrix descriptor for a K-major tile with 128-byte rows and the
-// 128-byte swizzle: 8-row groups are 1024 bytes apart; version 1 (Blackwell).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);                  // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                                  // leading byte offset (unused here)
-    d |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset
-    d |= (uint64_t)1 << 46;                                  // descriptor version
-    d |= (uint64_t)2 << 61;                                  // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: bf16 x bf16 -> f32, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                     uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
-                 ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-          "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
 
 template <int BN, int STAGES>
 struct Smem {
@@ -213,9 +164,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
         fence_barrier_init();
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
     }
     tc_fence_before();
     __syncthreads();
@@ -345,8 +294,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n"
-                     ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 

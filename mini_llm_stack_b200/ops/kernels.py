@@ -277,7 +277,9 @@ class Ops:
             fn = _decl(lib, "mls_attention_mma",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I,
                         _P, _P, _LL, _P, _I, _P])
-            self._attention_libs[hd] = fn
+            tc = _decl(lib, "mls_attention_tc",
+                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _LL, _P, _P])
+            self._attention_libs[hd] = (fn, tc)
 
     def _attention_plan(self, step, group: int, n_kv: int) -> tuple:
         """(64-row tiles, any small request, context splits) for a step: requests
@@ -288,12 +290,13 @@ class Ops:
         if plan is None:
             small = [q * group <= 16 for q in step.q_lens]
             n_tiles = sum((q * group + 63) // 64 for q, s in zip(step.q_lens, small) if not s)
+            n_tiles128 = sum((q * group + 127) // 128 for q, s in zip(step.q_lens, small) if not s)
             n_small = sum(small)
             n_split = 1
             if n_small:
                 longest = max(c for c, s in zip(step.ctx_lens, small) if s)
                 n_split = self.split_for(n_small, longest, n_kv)
-            plan = (n_tiles, 1 if n_small else 0, n_split)
+            plan = (n_tiles, 1 if n_small else 0, n_split, n_tiles128)
             step.attn_tiles[key] = plan
         return plan
 
@@ -337,9 +340,23 @@ class Ops:
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
         _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
         if qkv.dtype == torch.bfloat16 and self.attention_impl != "simt":
-            fn = self._attention_libs.get(hd)
-            _need(fn is not None, f"attention kernels for head size {hd} were not required")
-            n_tiles, n_small, n_split = self._attention_plan(step, n_heads // n_kv, n_kv)
+            fns = self._attention_libs.get(hd)
+            _need(fns is not None, f"attention kernels for head size {hd} were not required")
+            fn, tc = fns
+            n_tiles, n_small, n_split, n_tiles128 = self._attention_plan(step, n_heads // n_kv, n_kv)
+            if (n_tiles and hd in (64, 128) and g.block_size in (8, 16, 32, 64)
+                    and self.attention_impl == "auto"):
+                # prompts and portions: the tcgen05 kernel; what is left for the call
+                # below are the requests of a few rows
+                self.launches += 1
+                _check(tc(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
+                          _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
+                          step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
+                          n_tiles128, n_small, cache.k_pool.shape[0], _ptr(self.status),
+                          self._stream()), "attention_tc")
+                n_tiles = 0
+                if not n_small:
+                    return
             part_o = part_lse = None
             if n_split > 1:
                 units = t * n_heads

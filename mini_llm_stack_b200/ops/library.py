@@ -38,7 +38,7 @@ NVCC_FLAGS = [
 MODULES = {
     "core": ["embed.cu", "norm.cu", "rope_store.cu", "swiglu.cu", "gemm_f32.cu",
              "attention_simt.cu", "sampling.cu"],
-    "attention": ["attention_mma.cu"],
+    "attention": ["attention_mma.cu", "attention_tc.cu"],
     "gemm": ["gemm_tcgen05.cu"],
     "argmax_static": ["argmax_static.cu"],
 }
