@@ -6,14 +6,18 @@
 // scores, maxima, sums and accumulators; P rounded to bfloat16 for the second
 // product (kernels/attention_fwd.py:106).
 //
-// One CTA owns 128 rows, (token, head-in-group) pairs of one kv head, and walks the
-// keys 128 at a time:
-//   warp 0      brings keys and values in with TMA, one copy per page and 64-wide half;
+// One CTA owns 256 rows, (token, head-in-group) pairs of one kv head, as two chains
+// of 128 rows that share the keys and values and take turns on the tensor cores; it
+// walks the keys 64 at a time:
+//   warp 0      brings keys and values in with TMA, one copy per page and 64-wide half,
+//               four tiles ahead;
 //   warp 1      issues S = Q K^T and O += P V (tcgen05.mma), accumulators in TMEM;
-//   warps 2..5  one thread per row: read S from TMEM, scale, mask, exponentiate, write P
-//               to shared memory as the next product's operand, rescale O when the
-//               running maximum has grown by more than 2^8, and store O at the end.
-// S is double-buffered in TMEM so that the next tile's Q K^T runs during the softmax.
+//   warps 2..9  one thread per row (four warps a chain): read S from TMEM, scale, mask,
+//               exponentiate, write P to shared memory as the next product's operand,
+//               rescale O when the running maximum has grown by more than 2^8, and
+//               store O at the end.
+// Each chain's S is double-buffered in TMEM, so the next tile's Q K^T and the other
+// chain's products run during a chain's softmax.
 // Every wait is bounded and reports MLS_STATUS_TIMEOUT.
 #include "common.cuh"
 #include "tma.cuh"
@@ -32,24 +36,29 @@ using namespace mls_tma;
 using namespace mls_tc;
 
 constexpr int HD = MLS_HEAD_DIM;
-constexpr int ROWS = 128;                        // rows of a tile
-constexpr int BN = 128;                          // keys of a tile
+constexpr int CHAINS = 2;                        // row blocks of 128 that take turns on the tensor cores
+constexpr int ROWS = 128 * CHAINS;               // rows of a tile
+constexpr int BN = 64;                           // keys of a tile
 constexpr int HALVES = HD / 64;
 constexpr int BLOCK = 128 * 128;                 // bytes of [128 rows][64 elements]: 16 KB
-constexpr int Q_BYTES = HALVES * BLOCK;
-constexpr int P_BYTES = 2 * BLOCK;               // 128 keys = two 64-wide K blocks
-constexpr int KV_STAGE = 2 * HALVES * BLOCK;     // keys, then values
-constexpr int STAGES = 2;
-constexpr int THREADS = 192;
-constexpr int TMEM_COLS = 512;                   // S0 | S1 | O
-constexpr int COL_S = 0, COL_O = 2 * BN;
+constexpr int KBLOCK = BN * 128;                 // bytes of [64 keys][64 elements]: 8 KB
+constexpr int Q_BYTES = HALVES * BLOCK;          // per chain
+constexpr int P_BYTES = BLOCK;                   // per chain: [128 rows][64 keys]
+constexpr int KV_STAGE = 2 * HALVES * KBLOCK;    // keys, then values
+constexpr int STAGES = 4;
+constexpr int THREADS = 64 + 128 * CHAINS;
+constexpr int TMEM_COLS = 512;                   // per chain S0 | S1, then per chain O
+constexpr int COL_S = 0, COL_O = CHAINS * 2 * BN;
+static_assert(COL_O + CHAINS * HD <= TMEM_COLS, "tensor memory columns");
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;             // log2: P stays below 2^8
 
 // barrier slots
-constexpr int B_KV_FULL = 0, B_KV_EMPTY = 2, B_S_FULL = 4, B_S_EMPTY = 6, B_P_FULL = 8,
-              B_P_EMPTY = 9, B_Q_FULL = 10, N_BARS = 11;
-constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + STAGES * KV_STAGE + 8 * N_BARS + 16 + 1024;
+constexpr int B_KV_FULL = 0, B_KV_EMPTY = STAGES, B_S_FULL = 2 * STAGES,        // [chain][2]
+              B_S_EMPTY = B_S_FULL + 2 * CHAINS, B_P_FULL = B_S_EMPTY + 2 * CHAINS,   // [chain]
+              B_P_EMPTY = B_P_FULL + CHAINS, B_Q_FULL = B_P_EMPTY + CHAINS, N_BARS = B_Q_FULL + 1;
+// no alignment slack: two CTAs must fit one SM; the kernel checks the alignment
+constexpr int SMEM_BYTES = CHAINS * (Q_BYTES + P_BYTES) + STAGES * KV_STAGE + 8 * N_BARS + 16;
 
 struct Params {
     const __nv_bfloat16* qkv;
@@ -73,15 +82,20 @@ __device__ __forceinline__ bool is_small(int q_len, int group) { return q_len * 
 __device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
     return tile + (chunk >> 3) * BLOCK + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
+#define MLS_STATUS_BAD_SMEM 16       // dynamic shared memory is not 1024-byte aligned
 
 __global__ void __launch_bounds__(THREADS)
 attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    uint8_t* gbase = smem_raw + (base - raw);
-    const uint32_t q_smem = base, p_smem = base + Q_BYTES, kv_smem = p_smem + P_BYTES;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    if (base & 1023u) {                          // the swizzled tiles need this alignment
+        if (threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_SMEM);
+        return;
+    }
+    uint8_t* gbase = smem_raw;
+    const uint32_t q_smem = base, p_smem = base + CHAINS * Q_BYTES,
+                   kv_smem = p_smem + CHAINS * P_BYTES;
     const uint32_t bars = kv_smem + STAGES * KV_STAGE;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile uint32_t* tmem_slot =
@@ -115,12 +129,16 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar(B_KV_FULL + s), 1);
             mbar_init(bar(B_KV_EMPTY + s), 1);
+        }
+        for (int s = 0; s < 2 * CHAINS; ++s) {
             mbar_init(bar(B_S_FULL + s), 1);
             mbar_init(bar(B_S_EMPTY + s), 128);
         }
-        mbar_init(bar(B_P_FULL), 128);
-        mbar_init(bar(B_P_EMPTY), 1);
-        mbar_init(bar(B_Q_FULL), 128);
+        for (int c = 0; c < CHAINS; ++c) {
+            mbar_init(bar(B_P_FULL + c), 128);
+            mbar_init(bar(B_P_EMPTY + c), 1);
+        }
+        mbar_init(bar(B_Q_FULL), 128 * CHAINS);
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -158,7 +176,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                 for (int pi = 0; pi < ppt; ++pi) {
                     if ((mask >> pi) & 1u) continue;
                     for (int part = 0; part < 2 * HALVES; ++part) {
-                        const uint32_t dst = stage + part * BLOCK + pi * page_bytes;
+                        const uint32_t dst = stage + part * KBLOCK + pi * page_bytes;
                         for (uint32_t o = lane * 16; o < page_bytes; o += 512)
                             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(dst + o),
                                          "r"(0u) : "memory");
@@ -174,9 +192,9 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                 const int y = (page * P.n_kv + kvh) * bs;
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(stage + h * BLOCK + lane * page_bytes, &kmap, h * 64, y,
+                    tma_load_2d(stage + h * KBLOCK + lane * page_bytes, &kmap, h * 64, y,
                                 bar(B_KV_FULL + slot));
-                    tma_load_2d(stage + (HALVES + h) * BLOCK + lane * page_bytes, &vmap, h * 64, y,
+                    tma_load_2d(stage + (HALVES + h) * KBLOCK + lane * page_bytes, &vmap, h * 64, y,
                                 bar(B_KV_FULL + slot));
                 }
             }
@@ -186,49 +204,58 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(BN, 0);
             constexpr uint32_t idesc_o = umma_idesc(HD, 1);
-            auto issue_qk = [&](int j) -> bool {
+            // S(c, j) = Q_c K_j^T into chain c's score buffer j & 1
+            auto issue_qk = [&](int c, int j) -> bool {
                 const int slot = j % STAGES, sb = j & 1;
                 if (!mbar_wait(bar(B_KV_FULL + slot), (j / STAGES) & 1)) return false;
-                if (!mbar_wait(bar(B_S_EMPTY + sb), ((j >> 1) & 1) ^ 1)) return false;
+                if (!mbar_wait(bar(B_S_EMPTY + 2 * c + sb), ((j >> 1) & 1) ^ 1)) return false;
                 tc_fence_after();
                 const uint32_t k_src = kv_smem + slot * KV_STAGE;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * BLOCK + (kk & 3) * 32;
-                    umma(tmem + COL_S + sb * BN, umma_desc(q_smem + off), umma_desc(k_src + off),
-                         idesc_s, kk ? 1u : 0u);
+                    const uint32_t q_off = c * Q_BYTES + (kk >> 2) * BLOCK + (kk & 3) * 32;
+                    const uint32_t k_off = (kk >> 2) * KBLOCK + (kk & 3) * 32;
+                    umma(tmem + COL_S + (2 * c + sb) * BN, umma_desc(q_smem + q_off),
+                         umma_desc(k_src + k_off), idesc_s, kk ? 1u : 0u);
                 }
-                umma_commit(bar(B_S_FULL + sb));
+                umma_commit(bar(B_S_FULL + 2 * c + sb));
                 return true;
             };
             if (!mbar_wait(bar(B_Q_FULL), 0)) timed_out = true;
-            if (!timed_out && n_tiles > 0 && !issue_qk(0)) timed_out = true;
+            for (int c = 0; c < CHAINS && !timed_out && n_tiles > 0; ++c)
+                if (!issue_qk(c, 0)) timed_out = true;
             for (int j = 0; j < n_tiles && !timed_out; ++j) {
-                if (j + 1 < n_tiles && !issue_qk(j + 1)) {
-                    timed_out = true;
-                    break;
-                }
-                if (!mbar_wait(bar(B_P_FULL), j & 1)) {
-                    timed_out = true;
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t v_src = kv_smem + (j % STAGES) * KV_STAGE + HALVES * BLOCK;
+                for (int c = 0; c < CHAINS && !timed_out; ++c) {
+                    if (j + 1 < n_tiles && !issue_qk(c, j + 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    if (!mbar_wait(bar(B_P_FULL + c), j & 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t v_src = kv_smem + (j % STAGES) * KV_STAGE + HALVES * KBLOCK;
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint32_t p_off = (kk >> 2) * BLOCK + (kk & 3) * 32;
-                    umma(tmem + COL_O, umma_desc(p_smem + p_off),
-                         umma_desc_mn(v_src + kk * 16 * 128, BLOCK), idesc_o, (j | kk) ? 1u : 0u);
+                    for (int kk = 0; kk < BN / 16; ++kk)
+                        umma(tmem + COL_O + c * HD, umma_desc(p_smem + c * P_BYTES + kk * 32),
+                             umma_desc_mn(v_src + kk * 16 * 128, KBLOCK), idesc_o,
+                             (j | kk) ? 1u : 0u);
+                    umma_commit(bar(B_P_EMPTY + c));           // P_c is free, O_c holds tile j
                 }
-                umma_commit(bar(B_KV_EMPTY + (j % STAGES)));   // keys and values of tile j are done with
-                umma_commit(bar(B_P_EMPTY));                   // P is free, O holds tile j
+                umma_commit(bar(B_KV_EMPTY + (j % STAGES)));   // both chains are done with tile j
             }
         }
     } else {
         // ------------------------------------------------- softmax, correction, epilogue
         const int q = warp & 3;
-        const int row_in = q * 32 + lane;                      // row of the tile = TMEM lane
-        const int row = row0 + row_in;
+        const int c = (warp - 2) >> 2;                         // which chain
+        const int row_in = q * 32 + lane;                      // row of the chain = TMEM lane
+        const int row = row0 + c * 128 + row_in;
+        const uint32_t q_mine = q_smem + c * Q_BYTES, p_mine = p_smem + c * P_BYTES;
+        const int b_s_full = B_S_FULL + 2 * c, b_s_empty = B_S_EMPTY + 2 * c;
+        const int b_p_full = B_P_FULL + c, b_p_empty = B_P_EMPTY + c;
+        const uint32_t col_s = COL_S + 2 * c * BN, col_o = COL_O + c * HD;
         const bool live = row < rows;
         const int ti = live ? row / P.group : 0, g = live ? row - ti * P.group : 0;
         const int pos = live ? pos0 + ti : -1;
@@ -241,10 +268,10 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             const __nv_bfloat16* src =
                 P.qkv + (size_t)(tok0 + ti) * row_w + (size_t)(kvh * P.group + g) * HD;
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
+            for (int ch = 0; ch < HD / 8; ++ch) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (live) v = *reinterpret_cast<const uint4*>(src + c * 8);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(swz(q_smem, row_in, c)),
+                if (live) v = *reinterpret_cast<const uint4*>(src + ch * 8);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(swz(q_mine, row_in, ch)),
                              "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
             }
             fence_proxy_async();
@@ -255,14 +282,15 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         for (int j = 0; j < n_tiles && !timed_out; ++j) {
             const int sb = j & 1;
             const int kbase = kbase0 + j * BN;
-            if (!mbar_wait(bar(B_S_FULL + sb), (j >> 1) & 1)) {
+            if (!mbar_wait(bar(b_s_full + sb), (j >> 1) & 1)) {
                 timed_out = true;
                 break;
             }
             tc_fence_after();
-            const uint32_t s_addr = tmem + lane_base + COL_S + sb * BN;
-            // pass 1: the row's maximum over this tile
-            float m_tile = -INFINITY;
+            const uint32_t s_addr = tmem + lane_base + col_s + sb * BN;
+            // the whole row of scores into registers, scaled to the log2 domain; a key
+            // needs a mask only on the diagonal tiles and at a window's edge
+            float sc[BN];
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t a[16], b[16];
@@ -271,15 +299,23 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                 tmem_ld_wait();
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    const int ja = kbase + c0 + e, jb = ja + 16;
-                    if (ja <= pos && ja >= lo_row)
-                        m_tile = fmaxf(m_tile, __uint_as_float(a[e]) * P.scale_log2);
-                    if (jb <= pos && jb >= lo_row)
-                        m_tile = fmaxf(m_tile, __uint_as_float(b[e]) * P.scale_log2);
+                    sc[c0 + e] = __uint_as_float(a[e]) * P.scale_log2;
+                    sc[c0 + 16 + e] = __uint_as_float(b[e]) * P.scale_log2;
                 }
             }
+            const bool masked = kbase + BN - 1 > pos || kbase < lo_row;
+            if (__any_sync(0xffffffffu, masked)) {
+#pragma unroll
+                for (int e = 0; e < BN; ++e) {
+                    const int jj = kbase + e;
+                    if (jj > pos || jj < lo_row) sc[e] = -INFINITY;
+                }
+            }
+            float m_tile = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < BN; ++e) m_tile = fmaxf(m_tile, sc[e]);
             // P of the previous tile must have been consumed, and O must be at rest
-            if (j > 0 && !mbar_wait(bar(B_P_EMPTY), (j - 1) & 1)) {
+            if (j > 0 && !mbar_wait(bar(b_p_empty), (j - 1) & 1)) {
                 timed_out = true;
                 break;
             }
@@ -287,66 +323,54 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             const bool grow = m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > m_used);
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? m_tile : m_used;
-                const float c = (grow && m_used != -INFINITY) ? fast_exp2(m_used - m_new) : 1.0f;
+                const float cf = (grow && m_used != -INFINITY) ? fast_exp2(m_used - m_new) : 1.0f;
                 if (j > 0) {
-                    const uint32_t o_addr = tmem + lane_base + COL_O;
+                    const uint32_t o_addr = tmem + lane_base + col_o;
 #pragma unroll
-                    for (int c0 = 0; c0 < HD; c0 += 16) {
-                        uint32_t v[16];
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t v[16], w[16];
                         tmem_ld16(o_addr + c0, v);
+                        tmem_ld16(o_addr + c0 + 16, w);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * c);
+                        for (int e = 0; e < 16; ++e) {
+                            v[e] = __float_as_uint(__uint_as_float(v[e]) * cf);
+                            w[e] = __float_as_uint(__uint_as_float(w[e]) * cf);
+                        }
                         tmem_st16(o_addr + c0, v);
+                        tmem_st16(o_addr + c0 + 16, w);
                     }
                     tmem_st_wait();
                 }
-                l *= c;
+                l *= cf;
                 m_used = m_new;
             }
-            // pass 2: probabilities, their sum, and P as the next product's operand
+            // probabilities, their sum, and P as the next product's operand
             const float base_m = m_used == -INFINITY ? 0.f : m_used;
             float sum = 0.f;
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t a[16], b[16];
-                tmem_ld16(s_addr + c0, a);
-                tmem_ld16(s_addr + c0 + 16, b);
-                tmem_ld_wait();
-                uint32_t pk[16];
+            for (int ch = 0; ch < BN / 8; ++ch) {
+                uint32_t pk[4];
 #pragma unroll
-                for (int e = 0; e < 16; e += 2) {
-                    float p[4];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int ja = kbase + c0 + e + u, jb = ja + 16;
-                        p[u] = (ja <= pos && ja >= lo_row)
-                                   ? fast_exp2(__uint_as_float(a[e + u]) * P.scale_log2 - base_m) : 0.f;
-                        p[2 + u] = (jb <= pos && jb >= lo_row)
-                                       ? fast_exp2(__uint_as_float(b[e + u]) * P.scale_log2 - base_m) : 0.f;
-                    }
-                    sum += (p[0] + p[1]) + (p[2] + p[3]);
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(p[0], p[1]);
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(p[2], p[3]);
-                    pk[e >> 1] = *reinterpret_cast<uint32_t*>(&h0);
-                    pk[8 + (e >> 1)] = *reinterpret_cast<uint32_t*>(&h1);
+                for (int u = 0; u < 4; ++u) {
+                    const float p0 = fast_exp2(sc[ch * 8 + 2 * u] - base_m);
+                    const float p1 = fast_exp2(sc[ch * 8 + 2 * u + 1] - base_m);
+                    sum += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    pk[u] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                // keys c0 .. c0+31 of this row: four 16-byte chunks
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch)
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
-                                 ::"r"(swz(p_smem, row_in, (c0 >> 3) + ch)), "r"(pk[4 * ch]),
-                                   "r"(pk[4 * ch + 1]), "r"(pk[4 * ch + 2]), "r"(pk[4 * ch + 3])
-                                 : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
+                             ::"r"(swz(p_mine, row_in, ch)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
+                               "r"(pk[3]) : "memory");
             }
             l += sum;
             tc_fence_before();
             fence_proxy_async();
-            mbar_arrive(bar(B_S_EMPTY + sb));
-            mbar_arrive(bar(B_P_FULL));
+            mbar_arrive(bar(b_s_empty + sb));
+            mbar_arrive(bar(b_p_full));
         }
         // the last P V, then the row's output
-        if (!timed_out && n_tiles > 0 && !mbar_wait(bar(B_P_EMPTY), (n_tiles - 1) & 1))
+        if (!timed_out && n_tiles > 0 && !mbar_wait(bar(b_p_empty), (n_tiles - 1) & 1))
             timed_out = true;
         tc_fence_after();
         const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -355,7 +379,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 16) {
             uint32_t v[16];
-            tmem_ld16(tmem + lane_base + COL_O + c0, v);
+            tmem_ld16(tmem + lane_base + col_o + c0, v);
             tmem_ld_wait();
             if (live) {
                 uint32_t w[8];
@@ -403,7 +427,7 @@ bool pool_map(const void* pool, long long pool_rows, int block, CUtensorMap* out
 }  // namespace
 #endif
 
-// Prompts and portions of a step: n_tiles = number of 128-row tiles (requests that
+// Prompts and portions of a step: n_tiles = number of 256-row tiles (requests that
 // the split kernel takes are left out when skip_small is set).  Returns
 // MLS_ERR_UNSUPPORTED (and launches nothing) for head or page sizes it does not take.
 MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, const void* v_pool,

@@ -290,13 +290,13 @@ class Ops:
         if plan is None:
             small = [q * group <= 16 for q in step.q_lens]
             n_tiles = sum((q * group + 63) // 64 for q, s in zip(step.q_lens, small) if not s)
-            n_tiles128 = sum((q * group + 127) // 128 for q, s in zip(step.q_lens, small) if not s)
+            n_tiles_tc = sum((q * group + 255) // 256 for q, s in zip(step.q_lens, small) if not s)
             n_small = sum(small)
             n_split = 1
             if n_small:
                 longest = max(c for c, s in zip(step.ctx_lens, small) if s)
                 n_split = self.split_for(n_small, longest, n_kv)
-            plan = (n_tiles, 1 if n_small else 0, n_split, n_tiles128)
+            plan = (n_tiles, 1 if n_small else 0, n_split, n_tiles_tc)
             step.attn_tiles[key] = plan
         return plan
 
@@ -343,7 +343,7 @@ class Ops:
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
             fn, tc = fns
-            n_tiles, n_small, n_split, n_tiles128 = self._attention_plan(step, n_heads // n_kv, n_kv)
+            n_tiles, n_small, n_split, n_tiles_tc = self._attention_plan(step, n_heads // n_kv, n_kv)
             if (n_tiles and hd in (64, 128) and g.block_size in (8, 16, 32, 64)
                     and self.attention_impl == "auto"):
                 # prompts and portions: the tcgen05 kernel; what is left for the call
@@ -352,7 +352,7 @@ class Ops:
                 _check(tc(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
                           _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                           step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
-                          n_tiles128, n_small, cache.k_pool.shape[0], _ptr(self.status),
+                          n_tiles_tc, n_small, cache.k_pool.shape[0], _ptr(self.status),
                           self._stream()), "attention_tc")
                 n_tiles = 0
                 if not n_small:
