@@ -19,7 +19,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
 import statistics
 import subprocess
 import sys
@@ -29,7 +28,7 @@ from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 
-# BASELINE.json configs[2]: Llama-3-8B shape
+# the Llama-3-8B shape: 32 layers, hidden 4096, 32 / 8 heads of 128, feed-forward 14336
 MODEL = dict(architecture="llama_dense", vocab_size=128256, d_model=4096, n_layers=32,
              n_heads=32, n_kv_heads=8, head_dim=128, intermediate_size=14336,
              max_seq_len=8192, rope_theta=500000.0, norm_eps=1e-5, tie_embeddings=False,

@@ -32,6 +32,13 @@ class Engine:
         self._next_id = 0
         self.step_tokens: list = []
 
+    @classmethod
+    def from_options(cls, model, options) -> "Engine":
+        """An engine from an ``EngineOptions`` record."""
+        return cls(model, num_blocks=options.num_blocks, block_size=options.block_size,
+                   max_batch=options.max_batch, max_tokens_per_step=options.max_tokens_per_step,
+                   chunk_size=options.chunk_size, cuda_graphs=options.cuda_graphs)
+
     # the reference's attribute names
     @property
     def waiting(self):

@@ -13,10 +13,14 @@ from .runner import load_model, random_model
 
 
 class LLM:
-    def __init__(self, model, **engine_options):
+    def __init__(self, model, options=None, **engine_options):
+        """``options``: an ``EngineOptions`` record, or the engine's arguments by name."""
         self.model = model
         self.config = model.config
-        self.engine = Engine(model, **engine_options)
+        if options is not None:
+            self.engine = Engine.from_options(model, options)
+        else:
+            self.engine = Engine(model, **engine_options)
 
     @classmethod
     def from_folder(cls, folder, dtype: str | None = None, device="cuda:0",

@@ -73,7 +73,9 @@ def reference_logits(ref_root, cfg, w, tokens):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/mini-llm-stack")
+    ref_root = Path(sys.argv[1])
     for key in ("A", "B"):
         raw = CONFIGS[key]
         cfg = config_from_dict(dict(raw, dtype="float32"))
