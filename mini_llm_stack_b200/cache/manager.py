@@ -290,7 +290,19 @@ class CacheManager:
         """
         out = {}
         bs = self.block_size
-        rows = [self._records[o].row for o, _ in entries]
+        recs = [self._records[o] for o, _ in entries]
+        rows = [r.row for r in recs]
+        if all(n == 1 for _, n in entries):
+            # single decoded tokens: one gather instead of a loop over requests
+            rows_a = np.asarray(rows)
+            pos = np.fromiter((r.length for r in recs), dtype=np.int64, count=len(recs))
+            for g in self.paged:
+                pages = g.table[rows_a, pos // bs]
+                if pages.size and pages.min() < 0:
+                    raise CacheError("no page reserved for a token of this step")
+                out[g.gid] = (g.table[rows_a],
+                              (pages.astype(np.int64) * bs + pos % bs).astype(np.int32))
+            return out
         for g in self.paged:
             table = g.table[rows]
             slot_parts = []

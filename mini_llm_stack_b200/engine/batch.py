@@ -115,8 +115,11 @@ class BatchBuilder:
             b, n = off[name]
             return host[b:b + n]
 
-        tok = np.fromiter((x for e in entries for x in e.tokens), dtype=np.int64,
-                          count=t_total)
+        if t_total == r_total:
+            tok = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=t_total)
+        else:
+            tok = np.fromiter((x for e in entries for x in e.tokens), dtype=np.int64,
+                              count=t_total)
         if tok.size and (tok.min() < 0 or tok.max() >= self.vocab_size):
             raise BatchError(f"a token id lies outside the vocabulary of "
                              f"{self.vocab_size}")
@@ -129,11 +132,16 @@ class BatchBuilder:
         pos = view("positions")
         rot = view("req_of_token")
         outs = []
-        for r, e in enumerate(entries):
-            b, n = int(cu[r]), q_lens[r]
-            pos[b:b + n] = np.arange(ctx_lens[r] - n, ctx_lens[r])
-            rot[b:b + n] = r
-            outs.extend(b + w for w in e.want)
+        if t_total == r_total:                       # single tokens: no loop over requests
+            pos[:] = np.asarray(ctx_lens) - 1
+            rot[:] = np.arange(r_total)
+            outs = [r for r, e in enumerate(entries) if e.want]
+        else:
+            for r, e in enumerate(entries):
+                b, n = int(cu[r]), q_lens[r]
+                pos[b:b + n] = np.arange(ctx_lens[r] - n, ctx_lens[r])
+                rot[b:b + n] = r
+                outs.extend(b + w for w in e.want)
         if n_out:
             view("out_rows")[:] = outs
         else:

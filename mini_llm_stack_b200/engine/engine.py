@@ -72,7 +72,7 @@ class Engine:
         entries = []
         for p in plan.entries:
             r = p.request
-            toks = r.tokens[r.num_computed:r.num_computed + p.n_tokens]
+            toks = r.token_slice(r.num_computed, p.n_tokens)
             entries.append(Entry(r.req_id, toks, [p.n_tokens - 1] if p.wants_logits else []))
         logits = self.runner.step(entries)
         sampled = {}

@@ -29,6 +29,19 @@ class Request:
         return self.prompt + self.generated
 
     @property
+    def n_tokens(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+    def token_slice(self, start: int, n: int) -> list:
+        """``tokens[start:start + n]`` without building the whole list."""
+        p = len(self.prompt)
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        if start >= p:
+            return self.generated[start - p:start - p + n]
+        return self.prompt[start:] + self.generated[:start + n - p]
+
+    @property
     def remaining(self) -> int:
         """Tokens not yet run: the rest of the prompt, or the token sampled last."""
         return len(self.prompt) + len(self.generated) - self.num_computed

@@ -131,7 +131,7 @@ class Scheduler:
             req = self.waiting[0]
             if req in plan.preempted:
                 break                            # not in the step that preempted it
-            if not self.cache.can_hold(len(req.tokens) + 1, self.chunk_size):
+            if not self.cache.can_hold(req.n_tokens + 1, self.chunk_size):
                 break
             n = self._share(req, budget)
             if not self.cache.admit(req.req_id):
@@ -168,7 +168,7 @@ class Scheduler:
                 req.first_token_time = now
             if (len(req.generated) >= req.max_new_tokens                     # :219
                     or (req.eos_token is not None and tok == req.eos_token)  # :220
-                    or len(req.tokens) >= self.max_seq_len):                 # :221
+                    or req.n_tokens >= self.max_seq_len):                    # :221
                 req.state = FINISHED
                 req.finish_time = now
                 self.running.remove(req)
