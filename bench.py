@@ -68,7 +68,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "200"],
+                 "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -230,7 +230,6 @@ def main() -> int:
 
     mark0 = clocks.mark()
     ms, launches, mean_ctx = decode_run(args.batch, warmup, steps)
-    mark1 = clocks.mark()
     value = args.batch / ms * 1e3
     step_bytes = weight_bytes(raw, args.layers) + args.batch * mean_ctx * kv_bytes_per_token(
         raw, args.layers)
@@ -264,6 +263,7 @@ def main() -> int:
     e2e_tokens = sum(len(r.generated) for r in reqs) - n0
     assert len(engine.running) == args.batch and e2e_tokens == steps * args.batch
     h2d = runner.builder.last_bytes
+    mark2 = clocks.mark()
     clocks.stop()
 
     line = {
@@ -289,7 +289,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
-        "clocks": clocks.summary(mark0, mark1),
+        "clocks": clocks.summary(mark0, mark2),
     }
     print(json.dumps(line))
     return 0
