@@ -6,18 +6,16 @@
 // scores, maxima, sums and accumulators; P rounded to bfloat16 for the second
 // product (kernels/attention_fwd.py:106).
 //
-// One CTA owns 256 rows, (token, head-in-group) pairs of one kv head, as two chains
-// of 128 rows that share the keys and values and take turns on the tensor cores; it
-// walks the keys 64 at a time:
+// One CTA owns 128 rows, (token, head-in-group) pairs of one kv head, and walks the
+// keys 128 at a time (a tcgen05.mma costs about the same whatever its width, so
+// wide tiles pay):
 //   warp 0      brings keys and values in with TMA, one copy per page and 64-wide half,
-//               four tiles ahead;
+//               into a ring of three key tiles and a ring of two value tiles;
 //   warp 1      issues S = Q K^T and O += P V (tcgen05.mma), accumulators in TMEM;
-//   warps 2..9  one thread per row (four warps a chain): read S from TMEM, scale, mask,
-//               exponentiate, write P to shared memory as the next product's operand,
-//               rescale O when the running maximum has grown by more than 2^8, and
-//               store O at the end.
-// Each chain's S is double-buffered in TMEM, so the next tile's Q K^T and the other
-// chain's products run during a chain's softmax.
+//   warps 2..5  one thread per row: read S from TMEM, scale, mask, exponentiate, write P
+//               to shared memory as the next product's operand, rescale O when the
+//               running maximum has grown by more than 2^8, and store O at the end.
+// S is double-buffered in TMEM, so the next tile's Q K^T runs during the softmax.
 // Every wait is bounded and reports MLS_STATUS_TIMEOUT.
 #include "common.cuh"
 #include "tma.cuh"
@@ -36,16 +34,16 @@ using namespace mls_tma;
 using namespace mls_tc;
 
 constexpr int HD = MLS_HEAD_DIM;
-constexpr int CHAINS = 2;                        // row blocks of 128 that take turns on the tensor cores
+constexpr int CHAINS = 1;                        // row blocks of 128 a CTA owns
 constexpr int ROWS = 128 * CHAINS;               // rows of a tile
-constexpr int BN = 64;                           // keys of a tile
+constexpr int BN = 128;                          // keys of a tile: the wider a tcgen05.mma, the better
 constexpr int HALVES = HD / 64;
 constexpr int BLOCK = 128 * 128;                 // bytes of [128 rows][64 elements]: 16 KB
-constexpr int KBLOCK = BN * 128;                 // bytes of [64 keys][64 elements]: 8 KB
+constexpr int KBLOCK = BN * 128;                 // bytes of [128 keys][64 elements]: 16 KB
 constexpr int Q_BYTES = HALVES * BLOCK;          // per chain
-constexpr int P_BYTES = BLOCK;                   // per chain: [128 rows][64 keys]
-constexpr int KV_STAGE = 2 * HALVES * KBLOCK;    // keys, then values
-constexpr int STAGES = 4;
+constexpr int P_BYTES = (BN / 64) * BLOCK;       // per chain: [128 rows][128 keys]
+constexpr int K_STAGE = HALVES * KBLOCK, V_STAGE = HALVES * KBLOCK;
+constexpr int K_STAGES = 3, V_STAGES = 2;        // keys are needed a product earlier than values
 constexpr int THREADS = 64 + 128 * CHAINS;
 constexpr int TMEM_COLS = 512;                   // per chain S0 | S1, then per chain O
 constexpr int COL_S = 0, COL_O = CHAINS * 2 * BN;
@@ -54,11 +52,13 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;             // log2: P stays below 2^8
 
 // barrier slots
-constexpr int B_KV_FULL = 0, B_KV_EMPTY = STAGES, B_S_FULL = 2 * STAGES,        // [chain][2]
+constexpr int B_K_FULL = 0, B_K_EMPTY = K_STAGES, B_V_FULL = 2 * K_STAGES,
+              B_V_EMPTY = B_V_FULL + V_STAGES, B_S_FULL = B_V_EMPTY + V_STAGES,       // [chain][2]
               B_S_EMPTY = B_S_FULL + 2 * CHAINS, B_P_FULL = B_S_EMPTY + 2 * CHAINS,   // [chain]
               B_P_EMPTY = B_P_FULL + CHAINS, B_Q_FULL = B_P_EMPTY + CHAINS, N_BARS = B_Q_FULL + 1;
 // no alignment slack: two CTAs must fit one SM; the kernel checks the alignment
-constexpr int SMEM_BYTES = CHAINS * (Q_BYTES + P_BYTES) + STAGES * KV_STAGE + 8 * N_BARS + 16;
+constexpr int SMEM_BYTES = CHAINS * (Q_BYTES + P_BYTES) + K_STAGES * K_STAGE + V_STAGES * V_STAGE +
+                           8 * N_BARS + 16;
 
 struct Params {
     const __nv_bfloat16* qkv;
@@ -95,8 +95,8 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     }
     uint8_t* gbase = smem_raw;
     const uint32_t q_smem = base, p_smem = base + CHAINS * Q_BYTES,
-                   kv_smem = p_smem + CHAINS * P_BYTES;
-    const uint32_t bars = kv_smem + STAGES * KV_STAGE;
+                   k_smem = p_smem + CHAINS * P_BYTES, v_smem = k_smem + K_STAGES * K_STAGE;
+    const uint32_t bars = v_smem + V_STAGES * V_STAGE;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile uint32_t* tmem_slot =
         reinterpret_cast<volatile uint32_t*>(gbase + (bars - base) + 8 * N_BARS);
@@ -126,9 +126,13 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     const int n_tiles = (hi - kbase0) / BN + 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar(B_KV_FULL + s), 1);
-            mbar_init(bar(B_KV_EMPTY + s), 1);
+        for (int s = 0; s < K_STAGES; ++s) {
+            mbar_init(bar(B_K_FULL + s), 1);
+            mbar_init(bar(B_K_EMPTY + s), 1);
+        }
+        for (int s = 0; s < V_STAGES; ++s) {
+            mbar_init(bar(B_V_FULL + s), 1);
+            mbar_init(bar(B_V_EMPTY + s), 1);
         }
         for (int s = 0; s < 2 * CHAINS; ++s) {
             mbar_init(bar(B_S_FULL + s), 1);
@@ -152,14 +156,15 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         // -------------------------------------------------------------- TMA producer
         const int bs = P.block_size, ppt = BN / bs;
         const uint32_t page_bytes = bs * 128;
-        for (int t = 0; t < n_tiles; ++t) {
-            const int slot = t % STAGES;
-            if (!mbar_wait(bar(B_KV_EMPTY + slot), ((t / STAGES) & 1) ^ 1)) {
-                timed_out = true;
-                break;
-            }
+        // one ring for keys, one for values; `which` 0 = keys, 1 = values
+        auto load = [&](int t, int which) -> bool {
+            const int stages = which ? V_STAGES : K_STAGES;
+            const int slot = t % stages;
+            const uint32_t full = bar((which ? B_V_FULL : B_K_FULL) + slot);
+            const uint32_t empty = bar((which ? B_V_EMPTY : B_K_EMPTY) + slot);
+            if (!mbar_wait(empty, ((t / stages) & 1) ^ 1)) return false;
             const int kb = kbase0 + t * BN;
-            const uint32_t stage = kv_smem + slot * KV_STAGE;
+            const uint32_t stage = which ? v_smem + slot * V_STAGE : k_smem + slot * K_STAGE;
             bool valid = false;
             int page = -1;
             if (lane < ppt) {
@@ -175,7 +180,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                 // pages that are not keys of this request read as zeros
                 for (int pi = 0; pi < ppt; ++pi) {
                     if ((mask >> pi) & 1u) continue;
-                    for (int part = 0; part < 2 * HALVES; ++part) {
+                    for (int part = 0; part < HALVES; ++part) {
                         const uint32_t dst = stage + part * KBLOCK + pi * page_bytes;
                         for (uint32_t o = lane * 16; o < page_bytes; o += 512)
                             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(dst + o),
@@ -185,18 +190,21 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                 fence_proxy_async();
             }
             __syncwarp();
-            if (lane == 0)
-                mbar_arrive_expect_tx(bar(B_KV_FULL + slot), __popc(mask) * page_bytes * 2 * HALVES);
+            if (lane == 0) mbar_arrive_expect_tx(full, __popc(mask) * page_bytes * HALVES);
             __syncwarp();
             if (valid) {
                 const int y = (page * P.n_kv + kvh) * bs;
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(stage + h * KBLOCK + lane * page_bytes, &kmap, h * 64, y,
-                                bar(B_KV_FULL + slot));
-                    tma_load_2d(stage + (HALVES + h) * KBLOCK + lane * page_bytes, &vmap, h * 64, y,
-                                bar(B_KV_FULL + slot));
-                }
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_2d(stage + h * KBLOCK + lane * page_bytes, which ? &vmap : &kmap,
+                                h * 64, y, full);
+            }
+            return true;
+        };
+        for (int t = 0; t < n_tiles; ++t) {
+            if (!load(t, 0) || !load(t, 1)) {
+                timed_out = true;
+                break;
             }
         }
     } else if (warp == 1) {
@@ -206,11 +214,11 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             constexpr uint32_t idesc_o = umma_idesc(HD, 1);
             // S(c, j) = Q_c K_j^T into chain c's score buffer j & 1
             auto issue_qk = [&](int c, int j) -> bool {
-                const int slot = j % STAGES, sb = j & 1;
-                if (!mbar_wait(bar(B_KV_FULL + slot), (j / STAGES) & 1)) return false;
+                const int slot = j % K_STAGES, sb = j & 1;
+                if (!mbar_wait(bar(B_K_FULL + slot), (j / K_STAGES) & 1)) return false;
                 if (!mbar_wait(bar(B_S_EMPTY + 2 * c + sb), ((j >> 1) & 1) ^ 1)) return false;
                 tc_fence_after();
-                const uint32_t k_src = kv_smem + slot * KV_STAGE;
+                const uint32_t k_src = k_smem + slot * K_STAGE;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint32_t q_off = c * Q_BYTES + (kk >> 2) * BLOCK + (kk & 3) * 32;
@@ -219,6 +227,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                          umma_desc(k_src + k_off), idesc_s, kk ? 1u : 0u);
                 }
                 umma_commit(bar(B_S_FULL + 2 * c + sb));
+                if (c == CHAINS - 1) umma_commit(bar(B_K_EMPTY + slot));   // the keys are done with
                 return true;
             };
             if (!mbar_wait(bar(B_Q_FULL), 0)) timed_out = true;
@@ -234,16 +243,21 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                         timed_out = true;
                         break;
                     }
+                    if (c == 0 && !mbar_wait(bar(B_V_FULL + j % V_STAGES), (j / V_STAGES) & 1)) {
+                        timed_out = true;
+                        break;
+                    }
                     tc_fence_after();
-                    const uint32_t v_src = kv_smem + (j % STAGES) * KV_STAGE + HALVES * KBLOCK;
+                    const uint32_t v_src = v_smem + (j % V_STAGES) * V_STAGE;
 #pragma unroll
                     for (int kk = 0; kk < BN / 16; ++kk)
-                        umma(tmem + COL_O + c * HD, umma_desc(p_smem + c * P_BYTES + kk * 32),
+                        umma(tmem + COL_O + c * HD,
+                             umma_desc(p_smem + c * P_BYTES + (kk >> 2) * BLOCK + (kk & 3) * 32),
                              umma_desc_mn(v_src + kk * 16 * 128, KBLOCK), idesc_o,
                              (j | kk) ? 1u : 0u);
                     umma_commit(bar(B_P_EMPTY + c));           // P_c is free, O_c holds tile j
                 }
-                umma_commit(bar(B_KV_EMPTY + (j % STAGES)));   // both chains are done with tile j
+                umma_commit(bar(B_V_EMPTY + (j % V_STAGES)));  // the values of tile j are done with
             }
         }
     } else {
@@ -427,7 +441,16 @@ bool pool_map(const void* pool, long long pool_rows, int block, CUtensorMap* out
 }  // namespace
 #endif
 
-// Prompts and portions of a step: n_tiles = number of 256-row tiles (requests that
+// Rows of one tile of mls_attention_tc (0: this head size has no such kernel).
+MLS_API int mls_attention_tc_rows() {
+#if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
+    return ROWS;
+#else
+    return 0;
+#endif
+}
+
+// Prompts and portions of a step: n_tiles = number of tiles of mls_attention_tc_rows() rows (requests that
 // the split kernel takes are left out when skip_small is set).  Returns
 // MLS_ERR_UNSUPPORTED (and launches nothing) for head or page sizes it does not take.
 MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, const void* v_pool,

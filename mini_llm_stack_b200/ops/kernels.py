@@ -87,6 +87,7 @@ class Ops:
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
+        self._tc_rows = 128                      # rows of a tile of the tcgen05 attention kernel
         self._attention_shapes: set = set()      # (kv heads, group size) of the mixers
         self._scratch: dict = {}
         self._gemm = None
@@ -279,6 +280,9 @@ class Ops:
                         _P, _P, _LL, _P, _I, _P])
             tc = _decl(lib, "mls_attention_tc",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _LL, _P, _P])
+            rows_fn = lib.mls_attention_tc_rows
+            rows_fn.restype = ctypes.c_int
+            self._tc_rows = int(rows_fn()) or self._tc_rows
             self._attention_libs[hd] = (fn, tc)
 
     def _attention_plan(self, step, group: int, n_kv: int) -> tuple:
@@ -290,7 +294,9 @@ class Ops:
         if plan is None:
             small = [q * group <= 16 for q in step.q_lens]
             n_tiles = sum((q * group + 63) // 64 for q, s in zip(step.q_lens, small) if not s)
-            n_tiles_tc = sum((q * group + 255) // 256 for q, s in zip(step.q_lens, small) if not s)
+            rows = self._tc_rows
+            n_tiles_tc = sum((q * group + rows - 1) // rows
+                             for q, s in zip(step.q_lens, small) if not s)
             n_small = sum(small)
             n_split = 1
             if n_small:
