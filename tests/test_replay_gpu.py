@@ -150,6 +150,24 @@ def test_cutting_does_not_change_float32_bits_or_bf16_much(folders, dtype):
         assert_close(a, b, dtype, "bfloat16 whole against cut")
 
 
+def test_folder_stored_in_32_bits_run_in_bfloat16(tmp_path):
+    """Tensors stored in 32 bits stay 32-bit in a bfloat16 run: the activations are
+    bfloat16, the products with those weights true float32."""
+    folder, cfg, w = make_folder(tmp_path, "B", "float32", seed=11)
+    n = 90
+    toks = {"r": tokens_for(cfg["vocab_size"], n, 8)}
+    rp = Replayer(folder, "bfloat16", num_blocks=16)
+    model = rp.model
+    assert model.blocks[0].ffn.w_down.dtype == torch.float32
+    assert model.blocks[0].mixer.wqkv.dtype == torch.float32
+    assert model.runtime.act_dtype == torch.bfloat16
+    rp.step([("r", 60)], toks)
+    for _ in range(30):
+        rp.step([("r", 1)], toks)
+    assert_close(rp.logits("r"), plain_logits(w, cfg, toks["r"], "bfloat16"), "bfloat16",
+                 "float32 weights, bfloat16 activations")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_trace_run_program(folders, tmp_path, dtype):
     """The program itself: JSON lines in, ``done`` lines and .f32 files out."""
