@@ -34,6 +34,21 @@ class BatchError(ValueError):
     pass
 
 
+@dataclass
+class Prepared:
+    """A step laid out in a pinned buffer, not yet on the device."""
+    which: int
+    size: int
+    off: dict
+    groups: dict
+    t_total: int
+    r_total: int
+    n_out: int
+    q_lens: list
+    ctx_lens: list
+    owners: list
+
+
 def _align(n: int, a: int = 4) -> int:
     return (n + a - 1) // a * a
 
@@ -66,6 +81,15 @@ class BatchBuilder:
 
     def build(self, entries: list) -> StepContext:
         """Arrays for ``entries``; their pages must already be reserved."""
+        return self.submit(self.prepare(entries))
+
+    def prepare(self, entries: list) -> "Prepared":
+        """Lay the step's arrays out in a pinned buffer without sending them.
+
+        Everything but the token ids depends only on lengths and pages, so a step
+        of single decoded tokens can be prepared while the device still computes
+        the tokens it will be fed (``submit`` then takes the ids).
+        """
         if not entries:
             raise BatchError("a step needs at least one entry")
         cache = self.cache
@@ -150,13 +174,29 @@ class BatchBuilder:
             view(f"slot_map{gid}")[:] = slot_map
             view(f"table{gid}")[:] = table.reshape(-1)
 
+        return Prepared(which=which, size=cur, off=off, groups={g: t.shape[1] for g, (t, _) in groups.items()},
+                        t_total=t_total, r_total=r_total, n_out=n_out, q_lens=q_lens,
+                        ctx_lens=ctx_lens, owners=[e.owner for e in entries])
+
+    def submit(self, prep: "Prepared", token_ids=None) -> StepContext:
+        """Send a prepared step to the device; ``token_ids`` replaces the ids it was
+        prepared with (a step of single tokens whose ids were not yet known)."""
+        pinned = self._pinned[prep.which]
+        off, cur = prep.off, prep.size
+        if token_ids is not None:
+            tok = np.asarray(token_ids, dtype=np.int64)
+            if tok.size != prep.t_total or (tok.size and (tok.min() < 0 or
+                                                          tok.max() >= self.vocab_size)):
+                raise BatchError("token ids do not fit the prepared step or the vocabulary")
+            b, n = off["token_ids"]
+            pinned.numpy()[b:b + n] = tok
         dev = self._dev
         self.last_bytes = cur * 4
         if self.device.type == "cuda":
             dev[:cur].copy_(pinned[:cur], non_blocking=True)
-            ev = self._events[which] or torch.cuda.Event()
+            ev = self._events[prep.which] or torch.cuda.Event()
             ev.record(torch.cuda.current_stream(self.device))
-            self._events[which] = ev
+            self._events[prep.which] = ev
         else:
             dev[:cur].copy_(pinned[:cur])
 
@@ -164,17 +204,18 @@ class BatchBuilder:
             b, n = off[name]
             return dev[b:b + n]
 
+        r_total, t_total, n_out = prep.r_total, prep.t_total, prep.n_out
         gviews = {}
-        for gid, (table, _) in groups.items():
+        for gid, width in prep.groups.items():
             gviews[gid] = GroupView(
-                block_table=dview(f"table{gid}").view(r_total, table.shape[1]),
+                block_table=dview(f"table{gid}").view(r_total, width),
                 slot_map=dview(f"slot_map{gid}"),
-                block_size=cache.block_size, max_blocks=table.shape[1])
+                block_size=self.cache.block_size, max_blocks=width)
         return StepContext(
             n_tokens=t_total, n_requests=r_total,
             token_ids=dview("token_ids"), positions=dview("positions"),
             req_of_token=dview("req_of_token"), cu_q=dview("cu_q"),
             ctx_len=dview("ctx_len"), state_slot=dview("state_slot"),
             out_rows=dview("out_rows")[:n_out] if n_out else dview("out_rows")[:0],
-            n_out=n_out, groups=gviews, q_lens=q_lens, ctx_lens=ctx_lens,
-            max_q_len=max(q_lens), max_ctx_len=max(ctx_lens))
+            n_out=n_out, groups=gviews, q_lens=prep.q_lens, ctx_lens=prep.ctx_lens,
+            max_q_len=max(prep.q_lens), max_ctx_len=max(prep.ctx_lens))

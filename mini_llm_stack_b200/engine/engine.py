@@ -14,7 +14,7 @@ from ..sampling.sampler import Sampler, uniform_for
 from .batch import Entry
 from .request import Request
 from .runner import ModelRunner
-from .scheduler import Scheduler
+from .scheduler import Planned, Scheduler, StepPlan
 
 
 class Engine:
@@ -30,6 +30,7 @@ class Engine:
                                    self.max_seq_len)
         self.sampler = Sampler(model.runtime, max_rows=max_batch)
         self._next_id = 0
+        self._prepared = None                # (plan, arrays) of a step prepared ahead
         self.step_tokens: list = []
 
     @classmethod
@@ -65,27 +66,77 @@ class Engine:
         return req
 
     def step(self) -> bool:
-        """One scheduler iteration; True while work remains (serve/engine.py:229-256)."""
+        """One scheduler iteration; True while work remains (serve/engine.py:229-256).
+
+        While the device computes a step of single decoded tokens, the host lays
+        out the next step's arrays (they depend on lengths and pages, not on the
+        tokens being sampled); if nothing changed by the time the tokens are
+        known, the next step starts without planning or building.
+        """
         if not self.scheduler.has_work():
             return False
-        plan = self.scheduler.plan()
-        entries = []
-        for p in plan.entries:
-            r = p.request
-            toks = r.token_slice(r.num_computed, p.n_tokens)
-            entries.append(Entry(r.req_id, toks, [p.n_tokens - 1] if p.wants_logits else []))
-        logits = self.runner.step(entries)
+        ahead = self._take_prepared()
+        if ahead is not None:
+            plan, prepared = ahead
+            logits = self.runner.step_prepared(
+                prepared, [p.request.generated[-1] for p in plan.entries])
+        else:
+            plan = self.scheduler.plan()
+            entries = []
+            for p in plan.entries:
+                r = p.request
+                toks = r.token_slice(r.num_computed, p.n_tokens)
+                entries.append(Entry(r.req_id, toks, [p.n_tokens - 1] if p.wants_logits else []))
+            logits = self.runner.step(entries)
         sampled = {}
         if logits is not None:
             wanting = [p.request for p in plan.entries if p.wants_logits]
             temps = [r.temperature for r in wanting]
             us = [uniform_for(r.seed, r.req_id, len(r.generated)) if r.temperature > 0 else 0.0
                   for r in wanting]
-            toks = self.sampler.sample(logits, temps, us)
+            n = self.sampler.launch(logits, temps, us)
+            nxt = self._prepare_next(plan)          # host work under the device's
+            toks = self.sampler.finish(n)
             sampled = {r.req_id: t for r, t in zip(wanting, toks)}
-        self.scheduler.complete(plan, sampled)
+        else:
+            nxt = None
+        done = self.scheduler.complete(plan, sampled)
+        self._prepared = None if done else nxt
         self.step_tokens.append(plan.n_tokens)
         return self.scheduler.has_work()
+
+    def _prepare_next(self, plan):
+        """The next step's plan and arrays, if it is bound to be one more token for
+        exactly the requests of ``plan`` (none of them ends by count, nobody waits)."""
+        sch = self.scheduler
+        if sch.waiting or len(plan.entries) != len(sch.running) or plan.preempted:
+            return None
+        for p in plan.entries:
+            r = p.request
+            if (not p.wants_logits or len(r.generated) + 1 >= r.max_new_tokens
+                    or r.n_tokens + 1 >= self.max_seq_len):
+                return None
+        for p in plan.entries:
+            if not self.cache.reserve(p.request.req_id, 1):
+                return None                          # the usual path decides who gives way
+        nxt = StepPlan(entries=[Planned(p.request, 1, True) for p in plan.entries])
+        prepared = self.runner.builder.prepare(
+            [Entry(p.request.req_id, [0], [0]) for p in plan.entries])
+        return nxt, prepared
+
+    def _take_prepared(self):
+        """The step prepared ahead, if the world is still as it was assumed."""
+        ahead, self._prepared = self._prepared, None
+        if ahead is None:
+            return None
+        plan, _ = ahead
+        sch = self.scheduler
+        if sch.waiting or len(sch.running) != len(plan.entries):
+            return None
+        for p, r in zip(plan.entries, sch.running):
+            if p.request is not r or r.remaining != 1:
+                return None
+        return ahead
 
     def run_until_done(self, max_steps: int = 10_000) -> dict:
         t0 = time.perf_counter()

@@ -121,6 +121,20 @@ class ModelRunner:
         self.steps += 1
         return logits
 
+    @torch.no_grad()
+    def step_prepared(self, prepared, token_ids: list):
+        """``step`` for a batch of single tokens whose arrays were prepared ahead
+        (``BatchBuilder.prepare``) and whose token ids are known only now."""
+        ctx = self.builder.submit(prepared, token_ids)
+        if self.cuda_graphs and ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens:
+            logits = self._decode_from_graph(ctx)
+        else:
+            logits = self.model.forward(ctx, self.handles)
+        for owner in prepared.owners:
+            self.cache.commit(owner, 1)
+        self.steps += 1
+        return logits
+
     def _decode_from_graph(self, ctx):
         """A step of single decoded tokens, replayed from a CUDA graph.
 

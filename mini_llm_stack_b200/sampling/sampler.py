@@ -50,6 +50,10 @@ class Sampler:
 
     def sample(self, logits, temperatures: list, uniforms: list) -> list:
         """Tokens for ``logits [n, V]``; row i is greedy if ``temperatures[i] <= 0``."""
+        return self.finish(self.launch(logits, temperatures, uniforms))
+
+    def launch(self, logits, temperatures: list, uniforms: list) -> int:
+        """Start sampling and the copy of the tokens to the host; no wait."""
         n = logits.shape[0]
         self._grow(n)
         ops = self.runtime.ops
@@ -61,5 +65,9 @@ class Sampler:
         else:
             ops.sample(logits, None, None, self._out)
         self._out_host[:n].copy_(self._out[:n], non_blocking=True)
+        return n
+
+    def finish(self, n: int) -> list:
+        """Wait for the tokens of the last ``launch``."""
         torch.cuda.current_stream(self.runtime.device).synchronize()
         return self._out_host[:n].tolist()
