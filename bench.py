@@ -121,6 +121,105 @@ def prefill_flops(cfg, layers: int, t: int) -> float:
     return layers * (2.0 * lin * t + attn) + 2.0 * cfg["vocab_size"] * d
 
 
+# Llama-3.2-1B shape and Llama-2-7B shape, for the serving workloads
+MODEL_1B = dict(architecture="llama_dense", vocab_size=128256, d_model=2048, n_layers=16,
+                n_heads=32, n_kv_heads=8, head_dim=64, intermediate_size=8192, max_seq_len=8192,
+                rope_theta=500000.0, norm_eps=1e-5, tie_embeddings=True, dtype="bfloat16")
+MODEL_7B = dict(architecture="llama_dense", vocab_size=32000, d_model=4096, n_layers=32,
+                n_heads=32, n_kv_heads=32, head_dim=128, intermediate_size=11008,
+                max_seq_len=4096, rope_theta=10000.0, norm_eps=1e-5, tie_embeddings=False,
+                dtype="bfloat16")
+
+
+def serve_workload(name: str) -> int:
+    """Requests through the scheduler: chunked prompts beside decoding requests.
+
+    mixed_1b: 64 requests at once, prompts of 16..4096 tokens (log-uniform), 256 new
+    tokens each, Llama-3.2-1B shape.  poisson_7b: 128 requests arriving as a Poisson
+    process, prompts of 128..2048 tokens, 128..512 new tokens, Llama-2-7B shape, with
+    so few pages that requests are preempted and recomputed.
+    """
+    import random
+
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    from mini_llm_stack_b200.config import config_from_dict
+    from mini_llm_stack_b200.engine.engine import Engine
+    from mini_llm_stack_b200.engine.runner import random_model
+
+    rng = random.Random(7)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    if name == "mixed_1b":
+        raw, max_batch, budget, n_req = MODEL_1B, 64, 4096, 64
+        lens = [int(round(16 * (4096 / 16) ** rng.random())) for _ in range(n_req)]
+        outs = [256] * n_req
+        arrivals = [0.0] * n_req
+        num_blocks = sum((a + b) // PAGE + 2 for a, b in zip(lens, outs))
+    else:
+        raw, max_batch, budget, n_req = MODEL_7B, 64, 4096, 128
+        lens = [rng.randint(128, 2048) for _ in range(n_req)]
+        outs = [rng.randint(128, 512) for _ in range(n_req)]
+        t, arrivals = 0.0, []
+        for _ in range(n_req):
+            t += rng.expovariate(16.0)              # 16 requests a second
+            arrivals.append(t)
+        # room for about a third of the tokens all requests would hold at their ends
+        num_blocks = sum((a + b) // PAGE + 1 for a, b in zip(lens, outs)) // 3
+    cfg = config_from_dict(raw)
+    model = random_model(cfg, seed=0, device=dev, fast=True)
+    engine = Engine(model, num_blocks=num_blocks, block_size=PAGE, max_batch=max_batch,
+                    max_tokens_per_step=budget, chunk_size=2048)
+    gen = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lens]
+    # warm-up: compile, size buffers, capture graphs
+    for p in prompts[:2]:
+        engine.submit(p[:64], max_new_tokens=4)
+    engine.run_until_done()
+    engine.finished.clear()
+    engine.scheduler.preemptions = 0
+    engine.step_tokens.clear()
+
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    reqs, nxt = [], 0
+    while nxt < n_req or engine.scheduler.has_work():
+        now = time.perf_counter() - t0
+        while nxt < n_req and arrivals[nxt] <= now:
+            reqs.append(engine.submit(prompts[nxt], max_new_tokens=outs[nxt]))
+            nxt += 1
+        if engine.scheduler.has_work():
+            engine.step()
+        else:
+            time.sleep(max(0.0, arrivals[nxt] - now))
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    model.runtime.ops.check_status()
+    engine.cache.check()
+    assert all(len(r.generated) == o for r, o in zip(reqs, outs))
+    ttft = sorted(r.first_token_time - r.arrive_time for r in reqs)
+    tpot = sorted((r.finish_time - r.first_token_time) / max(1, len(r.generated) - 1) for r in reqs)
+    new_tokens = sum(outs)
+    line = {
+        "metric": f"served tokens/s, {name}", "value": round(new_tokens / wall, 1),
+        "unit": "tokens/s", "n_gpus": 1, "impl": "ours", "dtype": "bf16", "data": "synthetic",
+        "wall_s": round(wall, 3), "requests": n_req, "prompt_tokens": sum(lens),
+        "new_tokens": new_tokens, "steps": len(engine.step_tokens),
+        "mean_tokens_per_step": round(sum(engine.step_tokens) / len(engine.step_tokens), 1),
+        "preemptions": engine.scheduler.preemptions,
+        "ttft_s": {"p50": round(ttft[len(ttft) // 2], 4), "p99": round(ttft[-2], 4)},
+        "tpot_ms": {"p50": round(tpot[len(tpot) // 2] * 1e3, 3), "p99": round(tpot[-2] * 1e3, 3)},
+        "config": {"model": name, "layers": raw["n_layers"], "hidden": raw["d_model"],
+                   "heads": raw["n_heads"], "kv_heads": raw["n_kv_heads"],
+                   "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
+                   "vocab": raw["vocab_size"], "max_batch": max_batch, "token_budget": budget,
+                   "page_size": PAGE, "num_blocks": num_blocks},
+    }
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -131,6 +230,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=MODEL["max_seq_len"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed_1b", "poisson_7b"],
+                    help="decode: the contract's line; the others serve a request mix through "
+                         "the scheduler and print their own line")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -143,6 +245,8 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.workload != "decode":
+        return serve_workload(args.workload)
 
     import torch
 
