@@ -28,7 +28,7 @@ def make_folder(tmp_path, key: str, dtype: str, seed: int = 7, patch=None):
     cfg = config_from_dict(dict(raw, dtype=dtype))
     folder = tmp_path / f"tiny_{key}_{dtype}"
     write_random_model(folder, cfg, seed, NORM_STD[key])
-    w = {n: t.float() for n, t in load_file(str(folder / "model.safetensors")).items()}
+    w = {n: t.float().clone() for n, t in load_file(str(folder / "model.safetensors")).items()}
     return folder, plain_cfg(raw), w
 
 

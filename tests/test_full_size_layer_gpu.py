@@ -28,7 +28,7 @@ def big(tmp_path_factory):
     tmp = tmp_path_factory.mktemp("big")
     cfg = config_from_dict(dict(BIG, dtype="bfloat16"))
     write_random_model(tmp / "m", cfg, seed=4, norm_std=0.1)
-    w = {n: t.float() for n, t in load_file(str(tmp / "m" / "model.safetensors")).items()}
+    w = {n: t.float().clone() for n, t in load_file(str(tmp / "m" / "model.safetensors")).items()}
     return tmp / "m", plain_cfg(BIG), w
 
 

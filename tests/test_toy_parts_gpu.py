@@ -1,4 +1,5 @@
-"""Another mixer, with state of its own, registered and run from a test.
+"""Other parts, registered and run from a test: a mixer with state of its own, a
+routed feed-forward and a learned additive position encoding.
 
 The mixer, its architecture and its configuration are defined here; no file of
 the framework knows them.  The mixer keeps a fixed-size state per request (a
@@ -17,8 +18,8 @@ from engine_helpers import Replayer, assert_close, tokens_for
 from mini_llm_stack_b200.config import (config_from_folder, register_architecture,
                                         unregister_architecture)
 from mini_llm_stack_b200.parts import (ComposedModel, FixedState, GroupedQueryAttention,
-                                       LayerCall, Mixer, OutputHead, PreNormBlock, RMSNorm,
-                                       RotaryPosition, SwiGLUFeedForward, TensorSpec,
+                                       LayerCall, Mixer, OutputHead, Part, PreNormBlock,
+                                       RMSNorm, RotaryPosition, SwiGLUFeedForward, TensorSpec,
                                        TokenEmbedding)
 from mini_llm_stack_b200.weights import write_random_model
 from safetensors.torch import load_file
@@ -130,7 +131,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         cfg = ToyConfig()
         write_random_model(tmp_path / "toy", cfg, seed=2, norm_std=0.1)
         assert config_from_folder(tmp_path / "toy") == cfg
-        w = {n: t.float() for n, t in
+        w = {n: t.float().clone() for n, t in
              load_file(str(tmp_path / "toy" / "model.safetensors")).items()}
         rp = Replayer(tmp_path / "toy", "float32", num_blocks=12, max_requests=3)
         cache = rp.runner.cache
@@ -148,3 +149,160 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         assert cache.slots.num_free == 3
     finally:
         unregister_architecture("toy_decay")
+
+
+# ---------------------------------------------------------------------------------------
+# another feed-forward (routed) and another position encoding (learned, additive)
+# ---------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class ToyRoutedConfig:
+    architecture: str = "toy_routed"
+    vocab_size: int = 61
+    d_model: int = 64
+    n_layers: int = 2
+    n_heads: int = 2
+    head_dim: int = 32
+    intermediate_size: int = 48
+    n_experts: int = 3
+    max_seq_len: int = 96
+    norm_eps: float = 1e-5
+    dtype: str = "float32"
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**raw)
+
+    def to_dict(self):
+        return asdict(self)
+
+
+class RoutedFeedForward(Part):
+    """Top-1 routing: each token goes to the expert with the largest router logit and
+    is scaled by that expert's softmax weight.  The experts are the framework's SwiGLU."""
+
+    def __init__(self, d_model, inter, n_experts):
+        self.d, self.n = d_model, n_experts
+        self.experts = [SwiGLUFeedForward(d_model, inter) for _ in range(n_experts)]
+
+    def tensor_specs(self):
+        out = {"router.weight": TensorSpec((self.n, self.d))}
+        for e, ex in enumerate(self.experts):
+            out.update({f"experts.{e}.{n}": s for n, s in ex.tensor_specs().items()})
+        return out
+
+    def bind(self, tensors, runtime):
+        self.runtime = runtime
+        self.router = tensors["router.weight"].float()
+        for e, ex in enumerate(self.experts):
+            pre = f"experts.{e}."
+            ex.bind({n[len(pre):]: t for n, t in tensors.items() if n.startswith(pre)}, runtime)
+
+    def forward(self, h, step):
+        probs = torch.softmax(h.float() @ self.router.t(), dim=-1)      # float32 router
+        weight, choice = probs.max(dim=-1)
+        out = torch.zeros_like(h)
+        for e, ex in enumerate(self.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                y = ex.forward(h[rows].contiguous(), step)
+                out[rows] = (y.float() * weight[rows, None]).to(h.dtype)
+        return out
+
+
+class LearnedPositions(TokenEmbedding):
+    """``x[t] = E[token[t]] + Pos[position[t]]``: a position encoding added once."""
+
+    def __init__(self, vocab, d_model, max_pos):
+        super().__init__(vocab, d_model)
+        self.max_pos = max_pos
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.vocab_size, self.d_model)),
+                "positions": TensorSpec((self.max_pos, self.d_model))}
+
+    def bind(self, tensors, runtime):
+        super().bind({"weight": tensors["weight"]}, runtime)
+        self.table = tensors["positions"].float()
+
+    def forward(self, step):
+        x = super().forward(step)
+        x += self.table[step.positions.long()]
+        return x
+
+
+class NoRotation(RotaryPosition):
+    """Keys and values go into the pages unrotated: cos = 1, sin = 0."""
+
+    def bind(self, tensors, runtime):
+        self.runtime = runtime
+        self.cos = torch.ones(self.max_positions, self.head_dim // 2, device=runtime.device)
+        self.sin = torch.zeros(self.max_positions, self.head_dim // 2, device=runtime.device)
+
+
+def build_toy_routed(cfg):
+    emb = LearnedPositions(cfg.vocab_size, cfg.d_model, cfg.max_seq_len)
+    blocks = []
+    for _ in range(cfg.n_layers):
+        mixer = GroupedQueryAttention(cfg.d_model, cfg.n_heads, cfg.n_heads, cfg.head_dim,
+                                      cfg.head_dim ** -0.5,
+                                      NoRotation(cfg.head_dim, 1.0, cfg.max_seq_len))
+        blocks.append(PreNormBlock(RMSNorm(cfg.d_model, cfg.norm_eps), mixer,
+                                   RMSNorm(cfg.d_model, cfg.norm_eps),
+                                   RoutedFeedForward(cfg.d_model, cfg.intermediate_size,
+                                                     cfg.n_experts)))
+    calls = [LayerCall(i, i, True) for i in range(cfg.n_layers)]
+    return ComposedModel(cfg, emb, blocks, calls, RMSNorm(cfg.d_model, cfg.norm_eps),
+                         OutputHead(cfg.vocab_size, cfg.d_model, tied_to=None))
+
+
+def plain_toy_routed(w, cfg, tokens):
+    toks = torch.as_tensor(tokens)
+    S = len(tokens)
+    x = w["embed.weight"][toks] + w["embed.positions"][:S]
+    for i in range(cfg.n_layers):
+        p = f"blocks.{i}"
+        h = P.plain_rmsnorm(x, w[f"{p}.attn_norm.weight"], cfg.norm_eps)
+        H, hd = cfg.n_heads, cfg.head_dim
+        q = (h @ w[f"{p}.attn.wq.weight"].t()).view(S, H, hd).transpose(0, 1)
+        k = (h @ w[f"{p}.attn.wk.weight"].t()).view(S, H, hd).transpose(0, 1)
+        v = (h @ w[f"{p}.attn.wv.weight"].t()).view(S, H, hd).transpose(0, 1)
+        o = P.plain_attention(q, k, v, hd ** -0.5).transpose(0, 1).reshape(S, H * hd)
+        x = x + o @ w[f"{p}.attn.wo.weight"].t()
+        h = P.plain_rmsnorm(x, w[f"{p}.mlp_norm.weight"], cfg.norm_eps)
+        probs = torch.softmax(h @ w[f"{p}.mlp.router.weight"].t(), dim=-1)
+        weight, choice = probs.max(dim=-1)
+        y = torch.zeros_like(h)
+        for t in range(S):
+            e = int(choice[t])
+            pre = f"{p}.mlp.experts.{e}"
+            y[t] = weight[t] * P.plain_swiglu(h[t:t + 1], w[f"{pre}.w_gate.weight"],
+                                              w[f"{pre}.w_up.weight"], w[f"{pre}.w_down.weight"])[0]
+        x = x + y
+    return P.plain_rmsnorm(x, w["final_norm.weight"], cfg.norm_eps) @ w["lm_head.weight"].t()
+
+
+def test_routed_feed_forward_and_learned_positions_without_framework_changes(tmp_path):
+    from mini_llm_stack_b200.parts import Part  # noqa: F401  (the base the toy parts use)
+    register_architecture("toy_routed", ToyRoutedConfig, build_toy_routed)
+    try:
+        cfg = ToyRoutedConfig()
+        write_random_model(tmp_path / "routed", cfg, seed=5, norm_std=0.1)
+        w = {n: t.float().clone() for n, t in
+             load_file(str(tmp_path / "routed" / "model.safetensors")).items()}
+        w["embed.positions"] *= 10            # make the positions matter
+        from safetensors.torch import save_file
+        save_file({n: t.contiguous() for n, t in w.items()},
+                  str(tmp_path / "routed" / "model.safetensors"))
+        rp = Replayer(tmp_path / "routed", "float32", num_blocks=12, max_requests=3)
+        toks = {i: tokens_for(cfg.vocab_size, n, 80 + i) for i, n in enumerate([45, 30])}
+        rp.step([(0, 17), (1, 2)], toks)
+        rp.step([(0, 1), (1, 28)], toks, end=[1])
+        rp.step([(0, 27)], toks, end=[0])
+        for i in toks:
+            want = plain_toy_routed(w, cfg, toks[i])
+            assert_close(rp.logits(i), want, "float32", f"routed toy, request {i}")
+        # every expert is used by some token, or the test shows nothing about routing
+        h = torch.randn(200, cfg.d_model)
+        assert len(set((h @ w["blocks.0.mlp.router.weight"].t()).argmax(-1).tolist())) == cfg.n_experts
+    finally:
+        unregister_architecture("toy_routed")
