@@ -353,6 +353,25 @@ def test_one_far_key_among_hundreds_is_found(rts, dtype, far, ctx, q_len):
     assert (got - want).abs().max().item() <= tol * want.abs().max().item()
 
 
+@pytest.mark.parametrize("far, ctx, q_len", [(123, 8192, 1), (4097, 8192, 1), (77, 8192, 300),
+                                             (8000, 8192, 130)])
+def test_far_key_at_the_full_context_with_the_8b_heads(rts, far, ctx, q_len):
+    """The same at 8,192 keys with 32 query heads over 8 kv heads of 128: context
+    splits, many waves of tiles, the tcgen05 kernel's rings wrapping many times."""
+    case = AttnCase(rts[torch.bfloat16], 32, 8, 128, 16, [ctx], [q_len], seed=7)
+    q, k, v = case.q[0], case.k[0], case.v[0]
+    k.mul_(0.05)
+    direction = torch.ones(128, dtype=q.dtype, device=DEV)
+    q[:] = direction * 3
+    k[:, far] = direction * 3                      # 9 * 128 / 11.3 = 102 above all others
+    got = case.run()
+    rts[torch.bfloat16].ops.check_status()
+    mark = v[:, far].float().cpu().repeat_interleave(4, dim=0).reshape(1, -1)
+    visible = torch.arange(ctx - q_len, ctx) >= far
+    assert visible.all() or far > ctx - q_len
+    assert (got[visible] - mark).abs().max().item() < 3e-2
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window, ctx, q_len", [(10, 50, 1), (16, 64, 1), (40, 200, 30), (33, 100, 100),
                                                 (64, 1000, 1), (5, 300, 17)])
