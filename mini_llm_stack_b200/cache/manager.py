@@ -2,7 +2,8 @@
 
 Reference (serve/kv_cache.py:30-135): per layer a K and a V pool
 ``[num_blocks, n_heads, block_size, head_dim]`` (one (page, head) slab is
-contiguous), ``tables: seq -> [page ids]``, ``lens: seq -> tokens stored``, a
+contiguous; here the pools are ``[n_kv_heads, num_blocks, block_size, head_dim]``,
+so that consecutive pages of one kv head are one contiguous run as well), ``tables: seq -> [page ids]``, ``lens: seq -> tokens stored``, a
 LIFO free list; pages are claimed at admission (``allocate``) and one at a time
 at page boundaries (``append_slot``, :64-73), lengths advance once per step
 after all layers wrote (``set_len``, :85-88,107-108) and everything is given
@@ -42,7 +43,7 @@ class PagedGroup:
     spec: PagedKV
     members: list                     # cache slot indices, in order
     pool: PagePool
-    kv: torch.Tensor | None           # [members, 2, pages, Hkv, block, hd]
+    kv: torch.Tensor | None           # [members, 2, Hkv, pages, block, hd]
     table: np.ndarray                 # [max_requests, max_blocks] int32, -1 = none
 
 
@@ -102,7 +103,7 @@ class CacheManager:
         if allocate:
             for g in self.paged:
                 g.kv = torch.zeros(
-                    (len(g.members), 2, self.num_blocks, g.spec.n_kv_heads,
+                    (len(g.members), 2, g.spec.n_kv_heads, self.num_blocks,
                      self.block_size, g.spec.head_dim),
                     device=device, dtype=kv_dtype)
             for g in self.fixed:
@@ -340,6 +341,6 @@ class CacheManager:
                 ks.append(nan)
                 vs.append(nan)
             else:
-                ks.append(g.kv[m, 0, p, :, :take])
-                vs.append(g.kv[m, 1, p, :, :take])
+                ks.append(g.kv[m, 0, :, p, :take])
+                vs.append(g.kv[m, 1, :, p, :take])
         return torch.cat(ks, dim=1), torch.cat(vs, dim=1)

@@ -41,7 +41,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 struct Params {
     const __nv_bfloat16* qkv;            // [T, (H + 2 Hkv) * HD]
     __nv_bfloat16* out;                  // [T, H * HD]
-    const __nv_bfloat16* k_pool;         // [pages, Hkv, block, HD]
+    const __nv_bfloat16* k_pool;         // [Hkv, pages, block, HD]
     const __nv_bfloat16* v_pool;
     const int* block_table;              // [R, max_blocks], -1 = no page
     const int* cu_q;                     // [R + 1]
@@ -52,6 +52,7 @@ struct Params {
     int small_only;                      // tile kernel: 1 = skip requests the split kernel takes
     float scale_log2;                    // scale * log2(e)
     int* status;                         // device status word (a bounded wait that ran out)
+    long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -111,7 +112,7 @@ __device__ __forceinline__ void load_kv_tile(uint8_t* ks, uint8_t* vs, const Par
             const int page = table[j / P.block_size];
             ok = page >= 0;
             if (ok)
-                off = (((size_t)page * P.n_kv + kvh) * P.block_size + (j % P.block_size)) * HD +
+                off = (((size_t)kvh * P.n_pages + page) * P.block_size + (j % P.block_size)) * HD +
                       ch * 8;
         }
         cp_async16(ka + row * ROWB + ch * 16, P.k_pool + off, ok);
@@ -580,7 +581,7 @@ __device__ __forceinline__ void produce_tiles(const Params& P, const CUtensorMap
         if (lane == 0) mbar_arrive_expect_tx(full, __popc(mask) * page_bytes * 2 * HALVES);
         __syncwarp();
         if (valid) {
-            const int y = (page * P.n_kv + kvh) * bs;
+            const int y = (int)((kvh * P.n_pages + page) * bs);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) {
                 tma_load_2d(stage + h * HALF_BYTES + lane * page_bytes, kmap, h * 64, y, full);
@@ -1102,6 +1103,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     P.small_only = n_small ? 1 : 0;
     P.scale_log2 = scale * LOG2E;
     P.status = status;
+    P.n_pages = pool_pages;
     const bool tma_ok = use_tma && (block_size == 8 || block_size == 16 || block_size == 32 ||
                                     block_size == 64) && (HD % 64 == 0);
     (void)tma_ok;

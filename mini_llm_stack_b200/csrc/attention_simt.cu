@@ -62,7 +62,7 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
                       const int* __restrict__ block_table, int max_blocks,
                       const int* __restrict__ positions, const int* __restrict__ req_of_token,
                       int n_tokens, int n_heads, int n_kv, int hd, int block_size, float scale,
-                      int window) {
+                      int window, long long n_pages) {
     __shared__ float q_s[WARPS][MAX_HD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * WARPS + warp;   // (token, head)
@@ -92,7 +92,7 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
         float s = -INFINITY;
         if (valid) {
             const int page = table[j / block_size];
-            const T* kr = k_pool + (((size_t)page * n_kv + kvh) * block_size + j % block_size) * hd;
+            const T* kr = k_pool + (((size_t)kvh * n_pages + page) * block_size + j % block_size) * hd;
             s = dot_row(q_s[warp], kr, hd) * scale;
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -106,7 +106,7 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
             if (key < j_lo || key > p) continue;        // uniform across the warp
             const float pk = __shfl_sync(0xffffffffu, pj, jj);
             const int page = table[key / block_size];
-            const T* vr = v_pool + (((size_t)page * n_kv + kvh) * block_size + key % block_size) * hd;
+            const T* vr = v_pool + (((size_t)kvh * n_pages + page) * block_size + key % block_size) * hd;
 #pragma unroll
             for (int i = 0; i < MAX_HD / 32; ++i) {
                 const int dd = lane + 32 * i;
@@ -129,7 +129,7 @@ MLS_API int mls_attention_simt(const void* qkv, void* out, int dtype, const void
                                const void* v_pool, const int* block_table, int max_blocks,
                                const int* positions, const int* req_of_token, int n_tokens,
                                int n_heads, int n_kv, int hd, int block_size, float scale,
-                               int window, cudaStream_t stream) {
+                               int window, long long n_pages, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd > MAX_HD || hd <= 0 || n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
     const long long units = (long long)n_tokens * n_heads;
@@ -138,11 +138,11 @@ MLS_API int mls_attention_simt(const void* qkv, void* out, int dtype, const void
         attention_simt_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
             (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, block_table, max_blocks, positions, req_of_token,
-            n_tokens, n_heads, n_kv, hd, block_size, scale, window);
+            n_tokens, n_heads, n_kv, hd, block_size, scale, window, n_pages);
     else
         attention_simt_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
             (const float*)qkv, (float*)out, (const float*)k_pool, (const float*)v_pool,
             block_table, max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd,
-            block_size, scale, window);
+            block_size, scale, window, n_pages);
     return launch_status();
 }

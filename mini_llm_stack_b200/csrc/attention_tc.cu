@@ -69,6 +69,7 @@ struct Params {
     int max_blocks, n_req, n_heads, n_kv, group, block_size, window, small_only;
     float scale_log2;
     int* status;
+    long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -193,7 +194,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             if (lane == 0) mbar_arrive_expect_tx(full, __popc(mask) * page_bytes * HALVES);
             __syncwarp();
             if (valid) {
-                const int y = (page * P.n_kv + kvh) * bs;
+                const int y = (int)((kvh * P.n_pages + page) * bs);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)
                     tma_load_2d(stage + h * KBLOCK + lane * page_bytes, which ? &vmap : &kmap,
@@ -490,6 +491,7 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.small_only = skip_small ? 1 : 0;
     P.scale_log2 = scale * LOG2E;
     P.status = status;
+    P.n_pages = pool_pages;
     attention_tc_kernel<<<dim3(n_tiles, n_kv), THREADS, SMEM_BYTES, stream>>>(P, kmap, vmap);
     return launch_status();
 #else

@@ -8,7 +8,8 @@
 // operations (no fused multiply-add), as in the reference's expression.
 //
 // qkv: [T, (H + 2*Hkv) * hd], rows [q heads | k heads | v heads]; q is rotated in
-// place.  Pools: [pages, Hkv, block, hd]; slot = page * block + offset.
+// place.  Pools: [Hkv, pages, block, hd] (the pages of one kv head lie side by side);
+// slot = page * block + offset.
 #include "common.cuh"
 
 template <typename T>
@@ -35,6 +36,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         if (threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_SLOT);
     }
     const long long page = slot / block_size, off = slot % block_size;
+    const long long n_pages = pool_slots / block_size;
 
     const int rot_heads = n_heads + (writes ? n_kv : 0);
     for (int u = threadIdx.x; u < rot_heads * half; u += blockDim.x) {
@@ -49,7 +51,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
             Elem<T>::store(hp + i + half, o2);
         } else if (slot_ok) {
             const int kvh = head - n_heads;
-            T* dst = k_pool + (((size_t)page * n_kv + kvh) * block_size + off) * hd;
+            T* dst = k_pool + (((size_t)kvh * n_pages + page) * block_size + off) * hd;
             Elem<T>::store(dst + i, o1);
             Elem<T>::store(dst + i + half, o2);
         }
@@ -58,7 +60,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         const T* vsrc = row + (size_t)(n_heads + n_kv) * hd;
         for (int u = threadIdx.x; u < n_kv * hd; u += blockDim.x) {
             const int kvh = u / hd, i = u - kvh * hd;
-            v_pool[(((size_t)page * n_kv + kvh) * block_size + off) * hd + i] = vsrc[u];
+            v_pool[(((size_t)kvh * n_pages + page) * block_size + off) * hd + i] = vsrc[u];
         }
     }
 }
@@ -121,6 +123,7 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
     const bool slot_ok = slot >= 0 && slot < pool_slots;
     if (writes && !slot_ok && threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_SLOT);
     const long long page = slot / block_size, off = slot % block_size;
+    const long long n_pages = pool_slots / block_size;
 
     const int rot_units = (n_heads + (writes ? n_kv : 0)) * cph;
     const int v_units = writes ? n_kv * (hd / N) : 0;
@@ -142,7 +145,7 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
                 Vec16<T>::store(hp + half, o2);
             } else if (slot_ok) {
                 const int kvh = head - n_heads;
-                T* dst = k_pool + (((size_t)page * n_kv + kvh) * block_size + off) * hd + c * N;
+                T* dst = k_pool + (((size_t)kvh * n_pages + page) * block_size + off) * hd + c * N;
                 Vec16<T>::store(dst, o1);
                 Vec16<T>::store(dst + half, o2);
             }
@@ -153,7 +156,7 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
             const uint4 raw = *reinterpret_cast<const uint4*>(
                 row + (size_t)(n_heads + n_kv + kvh) * hd + c * N);
             *reinterpret_cast<uint4*>(
-                v_pool + (((size_t)page * n_kv + kvh) * block_size + off) * hd + c * N) = raw;
+                v_pool + (((size_t)kvh * n_pages + page) * block_size + off) * hd + c * N) = raw;
         }
     }
 }

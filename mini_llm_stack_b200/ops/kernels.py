@@ -82,7 +82,7 @@ class Ops:
                                   _LL, _I, _P, _P])
         self._attention_simt = _decl(core, "mls_attention_simt",
                                      [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _I, _P])
+                                      _I, _F, _I, _LL, _P])
         self._swiglu = _decl(core, "mls_swiglu", [_P, _P, _I, _I, _I, _P])
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -256,7 +256,7 @@ class Ops:
         _need(k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype,
               "rope_store: cache and activations differ in type")
         _need(k_pool.is_contiguous() and v_pool.is_contiguous(), "rope_store: pool layout")
-        pages, kvh, block, hd2 = k_pool.shape
+        kvh, pages, block, hd2 = k_pool.shape
         _need(kvh == n_kv and hd2 == hd, "rope_store: pool shape does not fit the heads")
         _need(cos.shape == (max_pos, hd // 2) and cos.dtype == torch.float32,
               "rope_store: bad tables")
@@ -358,7 +358,7 @@ class Ops:
                 _check(tc(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
                           _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                           step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
-                          n_tiles_tc, n_small, cache.k_pool.shape[0], _ptr(self.status),
+                          n_tiles_tc, n_small, cache.k_pool.shape[1], _ptr(self.status),
                           self._stream()), "attention_tc")
                 n_tiles = 0
                 if not n_small:
@@ -374,7 +374,7 @@ class Ops:
                       _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                       step.n_requests, t, n_heads, n_kv, g.block_size, float(scale), int(window),
                       n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse),
-                      cache.k_pool.shape[0], _ptr(self.status),
+                      cache.k_pool.shape[1], _ptr(self.status),
                       0 if self.attention_impl == "no_tma" else 1, self._stream()),
                    "attention_mma")
             return
@@ -382,8 +382,8 @@ class Ops:
         _check(self._attention_simt(
             _ptr(qkv), _ptr(out), _code(qkv.dtype), _ptr(cache.k_pool), _ptr(cache.v_pool),
             _ptr(g.block_table), g.max_blocks, _ptr(step.positions), _ptr(step.req_of_token),
-            t, n_heads, n_kv, hd, g.block_size, float(scale), int(window), self._stream()),
-            "attention_simt")
+            t, n_heads, n_kv, hd, g.block_size, float(scale), int(window),
+            cache.k_pool.shape[1], self._stream()), "attention_simt")
 
     def swiglu(self, gu, out) -> None:
         t, inter = out.shape

@@ -111,7 +111,7 @@ class StepContext:
 class CacheHandle:
     """What one layer call may touch of the cache.
 
-    paged: ``k_pool``/``v_pool`` [num_blocks, n_kv_heads, block_size, head_dim]
+    paged: ``k_pool``/``v_pool`` [n_kv_heads, num_blocks, block_size, head_dim]
     of this call's member of its group, ``group`` the id into
     ``StepContext.groups``, ``writes`` False if the call only reads a cache an
     earlier call filled.  fixed: ``state`` [max_slots, *shape].

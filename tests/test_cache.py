@@ -90,7 +90,7 @@ def test_groups_by_need_and_handles():
     assert [x.kind for x in h] == ["paged", "paged", "paged", "fixed", "paged", "none"]
     assert h[0].group == h[2].group == 0 and h[1].group == h[4].group == 1
     assert h[1].window == 10 and h[0].window is None
-    assert h[0].k_pool.shape == (6, 2, 4, 16) and h[3].state.shape == (3, 3, 5)
+    assert h[0].k_pool.shape == (2, 6, 4, 16) and h[3].state.shape == (3, 3, 5)
     # members of a group have memory of their own
     assert h[0].k_pool.data_ptr() != h[2].k_pool.data_ptr()
 

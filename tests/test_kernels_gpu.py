@@ -199,8 +199,8 @@ def test_rope_store(rts, dtype, heads, kv, hd, theta, block):
     qkv = rand((t, (heads + 2 * kv) * hd), dtype, 16)
     pos = torch.randint(0, max_pos, (t,), generator=torch.Generator().manual_seed(17)).int()
     slots = torch.randperm(pages * block, generator=torch.Generator().manual_seed(18))[:t].int()
-    k_pool = torch.full((pages, kv, block, hd), 7.0, dtype=dtype, device=DEV)
-    v_pool = torch.full((pages, kv, block, hd), 7.0, dtype=dtype, device=DEV)
+    k_pool = torch.full((kv, pages, block, hd), 7.0, dtype=dtype, device=DEV)
+    v_pool = torch.full((kv, pages, block, hd), 7.0, dtype=dtype, device=DEV)
     src = qkv.float().cpu()
     got = qkv.clone()
     ops.rope_store(got, pos.to(DEV), cos.to(DEV), sin.to(DEV), slots.to(DEV), k_pool, v_pool, t,
@@ -217,9 +217,9 @@ def test_rope_store(rts, dtype, heads, kv, hd, theta, block):
     touched = torch.zeros(pages, block, dtype=torch.bool)
     for i in range(t):
         pg, off = int(slots[i]) // block, int(slots[i]) % block
-        assert torch.equal(kp[pg, :, off], want_k[i]) and torch.equal(vp[pg, :, off], v[i])
+        assert torch.equal(kp[:, pg, off], want_k[i]) and torch.equal(vp[:, pg, off], v[i])
         touched[pg, off] = True
-    untouched = ~touched[:, None, :].expand(pages, kv, block)
+    untouched = ~touched[None, :, :].expand(kv, pages, block)
     assert bool((kp[untouched] == 7.0).all()) and bool((vp[untouched] == 7.0).all())
     # a call that reads another call's cache rotates its queries and writes nothing
     k2 = k_pool.clone()
@@ -265,8 +265,8 @@ class AttnCase:
             for j in range(c):
                 pg = pages[j // self.block]
                 if pg >= 0:
-                    self.handle.k_pool[pg, :, j % self.block] = self.k[i][:, j]
-                    self.handle.v_pool[pg, :, j % self.block] = self.v[i][:, j]
+                    self.handle.k_pool[:, pg, j % self.block] = self.k[i][:, j]
+                    self.handle.v_pool[:, pg, j % self.block] = self.v[i][:, j]
         step = BatchBuilder(cache, DEV, 10, 1 << 20).build(entries)
         t = step.n_tokens
         width = (self.heads + 2 * self.kv) * self.hd
