@@ -537,7 +537,8 @@ __device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
 // page and 64-wide half.  Stage `late_slot` (if any) is lent to the consumers at
 // the start and is first free after they have released it once.
 __device__ __forceinline__ void produce_tiles(const Params& P, const CUtensorMap* kmap,
-                                              const CUtensorMap* vmap, const int* table, int kvh,
+                                              const CUtensorMap* vmap, const CUtensorMap* kmap_wide,
+                                              const CUtensorMap* vmap_wide, const int* table, int kvh,
                                               int kb_first, int n_tiles, int lo, int hi,
                                               uint32_t base, uint32_t bar0, int late_slot) {
     const int lane = threadIdx.x & 31;
@@ -564,6 +565,19 @@ __device__ __forceinline__ void produce_tiles(const Params& P, const CUtensorMap
         }
         const unsigned mask = __ballot_sync(0xffffffffu, valid);
         const unsigned all = ppt >= 32 ? 0xffffffffu : ((1u << ppt) - 1u);
+        // pages that follow one another in the pool are one contiguous run of rows:
+        // a single wide copy per 64-wide half and tensor instead of one per page
+        const int first = __shfl_sync(0xffffffffu, page, 0);
+        if (mask == all && __all_sync(0xffffffffu, lane >= ppt || page == first + lane)) {
+            if (lane == 0) mbar_arrive_expect_tx(full, BN * 128 * 2 * HALVES);
+            __syncwarp();
+            if (lane < 2 * HALVES) {
+                const int h = lane % HALVES, is_v = lane / HALVES;
+                tma_load_2d(stage + lane * HALF_BYTES, is_v ? vmap_wide : kmap_wide, h * 64,
+                            (int)((kvh * P.n_pages + first) * bs), full);
+            }
+            continue;
+        }
         if (mask != all) {
             // pages that are not keys of this request read as zeros
             for (int pi = 0; pi < ppt; ++pi) {
@@ -594,7 +608,9 @@ __device__ __forceinline__ void produce_tiles(const Params& P, const CUtensorMap
 
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
-                           const __grid_constant__ CUtensorMap vmap) {
+                           const __grid_constant__ CUtensorMap vmap,
+                           const __grid_constant__ CUtensorMap kmap_wide,
+                           const __grid_constant__ CUtensorMap vmap_wide) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;       // the swizzle needs 1024-byte tiles
@@ -630,7 +646,8 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
     __syncthreads();
 
     if (warp == 4) {
-        produce_tiles(P, &kmap, &vmap, table, kvh, kbase0 + t_begin * BN, n_tiles, lo, hi, base,
+        produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kbase0 + t_begin * BN,
+                      n_tiles, lo, hi, base,
                       bar0, /*late_slot=*/-1);
         return;
     }
@@ -809,7 +826,9 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
 // ----------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
-                          const __grid_constant__ CUtensorMap vmap) {
+                          const __grid_constant__ CUtensorMap vmap,
+                          const __grid_constant__ CUtensorMap kmap_wide,
+                          const __grid_constant__ CUtensorMap vmap_wide) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -850,7 +869,8 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
     __syncthreads();
 
     if (warp == 4) {
-        produce_tiles(P, &kmap, &vmap, table, kvh, kbase0, n_tiles, lo, hi, base, bar0,
+        produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kbase0, n_tiles, lo, hi,
+                      base, bar0,
                       /*late_slot=*/TSTAGES - 1);
         return;
     }
@@ -1108,7 +1128,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
                                     block_size == 64) && (HD % 64 == 0);
     (void)tma_ok;
 #if MLS_HEAD_DIM % 64 == 0
-    CUtensorMap kmap, vmap;
+    CUtensorMap kmap, vmap, kmap_wide, vmap_wide;
     if (tma_ok) {
         static bool tma_configured = false;
         if (!tma_configured) {
@@ -1123,7 +1143,8 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
             tma_configured = true;
         }
         const long long rows = pool_pages * n_kv * block_size;
-        if (!pool_map(k_pool, rows, block_size, &kmap) || !pool_map(v_pool, rows, block_size, &vmap))
+        if (!pool_map(k_pool, rows, block_size, &kmap) || !pool_map(v_pool, rows, block_size, &vmap) ||
+            !pool_map(k_pool, rows, BN, &kmap_wide) || !pool_map(v_pool, rows, BN, &vmap_wide))
             return MLS_ERR_TENSOR_MAP;
     }
 #endif
@@ -1131,7 +1152,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
 #if MLS_HEAD_DIM % 64 == 0
         if (tma_ok)
             attention_tile_tma_kernel<<<dim3(n_tiles, n_kv), TMA_THREADS, TILE_TMA_SMEM, stream>>>(
-                P, kmap, vmap);
+                P, kmap, vmap, kmap_wide, vmap_wide);
         else
 #endif
             attention_tile_kernel<<<dim3(n_tiles, n_kv), NT, TILE_SMEM, stream>>>(P);
@@ -1142,7 +1163,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
 #if MLS_HEAD_DIM % 64 == 0
         if (tma_ok)
             attention_split_tma_kernel<<<dim3(n_req, n_kv, n_split), TMA_THREADS, TMA_SMEM,
-                                         stream>>>(P, kmap, vmap);
+                                         stream>>>(P, kmap, vmap, kmap_wide, vmap_wide);
         else
 #endif
             attention_split_kernel<<<dim3(n_req, n_kv, n_split), NT, SPLIT_SMEM, stream>>>(P);

@@ -87,7 +87,9 @@ __device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
 
 __global__ void __launch_bounds__(THREADS)
 attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
-                    const __grid_constant__ CUtensorMap vmap) {
+                    const __grid_constant__ CUtensorMap vmap,
+                    const __grid_constant__ CUtensorMap kmap_wide,
+                    const __grid_constant__ CUtensorMap vmap_wide) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {                          // the swizzled tiles need this alignment
@@ -177,6 +179,17 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             }
             const unsigned mask = __ballot_sync(0xffffffffu, valid);
             const unsigned all = ppt >= 32 ? 0xffffffffu : ((1u << ppt) - 1u);
+            // pages that follow one another in the pool are one contiguous run of
+            // rows: a single wide copy per 64-wide half instead of one per page
+            const int first = __shfl_sync(0xffffffffu, page, 0);
+            if (mask == all && __all_sync(0xffffffffu, lane >= ppt || page == first + lane)) {
+                if (lane == 0) mbar_arrive_expect_tx(full, BN * 128 * HALVES);
+                __syncwarp();
+                if (lane < HALVES)
+                    tma_load_2d(stage + lane * KBLOCK, which ? &vmap_wide : &kmap_wide, lane * 64,
+                                (int)((kvh * P.n_pages + first) * bs), full);
+                return true;
+            }
             if (mask != all) {
                 // pages that are not keys of this request read as zeros
                 for (int pi = 0; pi < ppt; ++pi) {
@@ -471,9 +484,10 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    CUtensorMap kmap, vmap;
+    CUtensorMap kmap, vmap, kmap_wide, vmap_wide;
     const long long rows = pool_pages * n_kv * block_size;
-    if (!pool_map(k_pool, rows, block_size, &kmap) || !pool_map(v_pool, rows, block_size, &vmap))
+    if (!pool_map(k_pool, rows, block_size, &kmap) || !pool_map(v_pool, rows, block_size, &vmap) ||
+        !pool_map(k_pool, rows, BN, &kmap_wide) || !pool_map(v_pool, rows, BN, &vmap_wide))
         return MLS_ERR_TENSOR_MAP;
     Params P;
     P.qkv = (const __nv_bfloat16*)qkv;
@@ -492,7 +506,8 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.scale_log2 = scale * LOG2E;
     P.status = status;
     P.n_pages = pool_pages;
-    attention_tc_kernel<<<dim3(n_tiles, n_kv), THREADS, SMEM_BYTES, stream>>>(P, kmap, vmap);
+    attention_tc_kernel<<<dim3(n_tiles, n_kv), THREADS, SMEM_BYTES, stream>>>(P, kmap, vmap, kmap_wide,
+                                                                          vmap_wide);
     return launch_status();
 #else
     return MLS_ERR_UNSUPPORTED;
