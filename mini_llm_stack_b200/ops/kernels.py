@@ -325,16 +325,20 @@ class Ops:
 
         Two CTAs of the split kernel fit an SM, so 296 run at a time; the cost of
         a choice is its number of such waves times the 64-key tiles a CTA walks
-        (plus two tiles' worth of start-up and merge).  The cheapest choice wins;
-        a split is never shorter than 256 keys.
+        (plus six tiles' worth of start-up), plus the merge kernel's time, which
+        grows with the number of parts (measured at batch 1: 16 parts beat 32).
+        The cheapest choice wins; a split is never shorter than 256 keys.
         """
+        forced = os.environ.get("MLS_B200_SPLITS")
+        if forced:
+            return max(1, min(int(forced), max(1, longest // 64)))
         slots = 2 * 148
         pairs = max(1, n_small * n_kv)
         tiles = -(-longest // 64)
         best, best_cost = 1, None
         for s in range(1, max(1, min(64, longest // 256)) + 1):
             waves = -(-pairs * s // slots)
-            cost = waves * (-(-tiles // s) + 2)
+            cost = waves * (-(-tiles // s) + 6) + (0.3 * s if s > 1 else 0.0)
             if best_cost is None or cost < best_cost:
                 best, best_cost = s, cost
         return best
