@@ -142,6 +142,8 @@ __device__ __forceinline__ void load_q_rows(uint8_t* qs, const Params& P, int to
 // 64 rows per CTA, 16 per warp
 // ----------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
+    chain_release();
+    chain_wait();
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* qs = smem;                               // [64][ROWB]
     uint8_t* kbuf = smem + TILE_BYTES;                // 2 x [64][ROWB]
@@ -306,6 +308,8 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
 constexpr int STAGES = 3;
 
 __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
+    chain_release();
+    chain_wait();
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* qs = smem;                               // [16][ROWB]
     uint8_t* kbuf = smem + 16 * ROWB;                 // STAGES x [64][ROWB]
@@ -491,6 +495,8 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
 // out[unit] = sum_s w_s part_o[s, unit] with w_s = 2^(lse_s - max lse) normalised.
 // One block per (token, head), one thread per element of the head.
 __global__ void attention_merge_kernel(const Params P) {
+    chain_release();
+    chain_wait();
     const int t = blockIdx.x, h = blockIdx.y;
     // only the requests the split kernel took have partial results
     int r = 0;
@@ -534,17 +540,18 @@ __device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
 
 // The producer warp: for every 64-key tile, wait until its stage is free, then
 // bring in the keys and values of the tile's pages with one bulk tensor copy per
-// page and 64-wide half.  Stage `late_slot` (if any) is lent to the consumers at
-// the start and is first free after they have released it once.
+// page and 64-wide half, for tiles t_from .. t_to - 1.  Stage `late_slot` (if any)
+// is lent to the consumers at the start and is first free after they have released
+// it once.
 __device__ __forceinline__ void produce_tiles(const Params& P, const CUtensorMap* kmap,
                                               const CUtensorMap* vmap, const CUtensorMap* kmap_wide,
                                               const CUtensorMap* vmap_wide, const int* table, int kvh,
-                                              int kb_first, int n_tiles, int lo, int hi,
+                                              int kb_first, int t_from, int t_to, int lo, int hi,
                                               uint32_t base, uint32_t bar0, int late_slot) {
     const int lane = threadIdx.x & 31;
     const int bs = P.block_size, ppt = BN / bs;
     const uint32_t page_bytes = bs * 128;
-    for (int t = 0; t < n_tiles; ++t) {
+    for (int t = t_from; t < t_to; ++t) {
         const int slot = t % TSTAGES, round = t / TSTAGES;
         const uint32_t full = bar0 + 8u * slot, empty = bar0 + 8u * (TSTAGES + slot);
         const uint32_t parity = slot == late_slot ? (round & 1) : ((round & 1) ^ 1);
@@ -611,6 +618,10 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
                            const __grid_constant__ CUtensorMap vmap,
                            const __grid_constant__ CUtensorMap kmap_wide,
                            const __grid_constant__ CUtensorMap vmap_wide) {
+    // The step's index arrays were copied before the step's first kernel began, so
+    // they may be read at once; what earlier kernels of this step write (the new
+    // tokens' queries, keys and values) is read after chain_wait.
+    chain_release();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;       // the swizzle needs 1024-byte tiles
@@ -622,7 +633,10 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
 
     const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int q_len = P.cu_q[r + 1] - P.cu_q[r];
-    if (!is_small(q_len, P.group)) return;
+    if (!is_small(q_len, P.group)) {
+        chain_wait();
+        return;
+    }
     const int rows = q_len * P.group;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
@@ -646,11 +660,20 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
     __syncthreads();
 
     if (warp == 4) {
-        produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kbase0 + t_begin * BN,
-                      n_tiles, lo, hi, base,
-                      bar0, /*late_slot=*/-1);
+        // Tiles that end before this request's first new token hold keys of earlier
+        // steps only: the first ring of them is asked for while the kernels that
+        // write the new token may still run.
+        const int kb_first = kbase0 + t_begin * BN;
+        const int old_tiles = max(0, (pos0 - kb_first) / BN);
+        const int ahead = min(min(n_tiles, TSTAGES), old_tiles);
+        produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kb_first, 0, ahead, lo,
+                      hi, base, bar0, /*late_slot=*/-1);
+        chain_wait();
+        produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kb_first, ahead,
+                      n_tiles, lo, hi, base, bar0, /*late_slot=*/-1);
         return;
     }
+    chain_wait();
 
     // --------------------------------------------------------------------- consumers
     const int rA = lane >> 2, rB = rA + 8;
@@ -829,6 +852,8 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
                           const __grid_constant__ CUtensorMap vmap,
                           const __grid_constant__ CUtensorMap kmap_wide,
                           const __grid_constant__ CUtensorMap vmap_wide) {
+    chain_release();
+    chain_wait();
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -869,9 +894,8 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
     __syncthreads();
 
     if (warp == 4) {
-        produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kbase0, n_tiles, lo, hi,
-                      base, bar0,
-                      /*late_slot=*/TSTAGES - 1);
+        produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kbase0, 0, n_tiles, lo,
+                      hi, base, bar0, /*late_slot=*/TSTAGES - 1);
         return;
     }
 
@@ -1151,26 +1175,29 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     if (n_tiles > 0) {
 #if MLS_HEAD_DIM % 64 == 0
         if (tma_ok)
-            attention_tile_tma_kernel<<<dim3(n_tiles, n_kv), TMA_THREADS, TILE_TMA_SMEM, stream>>>(
-                P, kmap, vmap, kmap_wide, vmap_wide);
+            MLS_LAUNCH((attention_tile_tma_kernel), dim3(n_tiles, n_kv), dim3(TMA_THREADS),
+                       TILE_TMA_SMEM, stream, P, kmap, vmap, kmap_wide, vmap_wide);
         else
 #endif
-            attention_tile_kernel<<<dim3(n_tiles, n_kv), NT, TILE_SMEM, stream>>>(P);
+            MLS_LAUNCH((attention_tile_kernel), dim3(n_tiles, n_kv), dim3(NT), TILE_SMEM, stream,
+                       P);
         int rc = launch_status();
         if (rc) return rc;
     }
     if (n_small) {
 #if MLS_HEAD_DIM % 64 == 0
         if (tma_ok)
-            attention_split_tma_kernel<<<dim3(n_req, n_kv, n_split), TMA_THREADS, TMA_SMEM,
-                                         stream>>>(P, kmap, vmap, kmap_wide, vmap_wide);
+            MLS_LAUNCH((attention_split_tma_kernel), dim3(n_req, n_kv, n_split), dim3(TMA_THREADS),
+                       TMA_SMEM, stream, P, kmap, vmap, kmap_wide, vmap_wide);
         else
 #endif
-            attention_split_kernel<<<dim3(n_req, n_kv, n_split), NT, SPLIT_SMEM, stream>>>(P);
+            MLS_LAUNCH((attention_split_kernel), dim3(n_req, n_kv, n_split), dim3(NT), SPLIT_SMEM,
+                       stream, P);
         int rc = launch_status();
         if (rc) return rc;
         if (n_split > 1) {
-            attention_merge_kernel<<<dim3(n_tokens, n_heads), HD < 128 ? HD : 128, 0, stream>>>(P);
+            MLS_LAUNCH((attention_merge_kernel), dim3(n_tokens, n_heads), dim3(HD < 128 ? HD : 128),
+                       0, stream, P);
             rc = launch_status();
             if (rc) return rc;
         }

@@ -63,6 +63,8 @@ attention_simt_kernel(const T* __restrict__ qkv, T* __restrict__ out,
                       const int* __restrict__ positions, const int* __restrict__ req_of_token,
                       int n_tokens, int n_heads, int n_kv, int hd, int block_size, float scale,
                       int window, long long n_pages) {
+    chain_release();
+    chain_wait();
     __shared__ float q_s[WARPS][MAX_HD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * WARPS + warp;   // (token, head)
@@ -135,14 +137,15 @@ MLS_API int mls_attention_simt(const void* qkv, void* out, int dtype, const void
     const long long units = (long long)n_tokens * n_heads;
     const int blocks = (int)((units + WARPS - 1) / WARPS);
     if (dtype == MLS_BF16)
-        attention_simt_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
-            (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
-            (const __nv_bfloat16*)v_pool, block_table, max_blocks, positions, req_of_token,
-            n_tokens, n_heads, n_kv, hd, block_size, scale, window, n_pages);
+        MLS_LAUNCH((attention_simt_kernel<__nv_bfloat16>), dim3(blocks), dim3(WARPS * 32), 0,
+                   stream, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out,
+                   (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table,
+                   max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd, block_size,
+                   scale, window, n_pages);
     else
-        attention_simt_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
-            (const float*)qkv, (float*)out, (const float*)k_pool, (const float*)v_pool,
-            block_table, max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd,
-            block_size, scale, window, n_pages);
+        MLS_LAUNCH((attention_simt_kernel<float>), dim3(blocks), dim3(WARPS * 32), 0, stream,
+                   (const float*)qkv, (float*)out, (const float*)k_pool, (const float*)v_pool,
+                   block_table, max_blocks, positions, req_of_token, n_tokens, n_heads, n_kv, hd,
+                   block_size, scale, window, n_pages);
     return launch_status();
 }

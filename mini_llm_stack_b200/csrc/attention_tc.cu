@@ -90,6 +90,8 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap,
                     const __grid_constant__ CUtensorMap kmap_wide,
                     const __grid_constant__ CUtensorMap vmap_wide) {
+    chain_release();
+    chain_wait();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {                          // the swizzled tiles need this alignment
@@ -506,8 +508,8 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.scale_log2 = scale * LOG2E;
     P.status = status;
     P.n_pages = pool_pages;
-    attention_tc_kernel<<<dim3(n_tiles, n_kv), THREADS, SMEM_BYTES, stream>>>(P, kmap, vmap, kmap_wide,
-                                                                          vmap_wide);
+    MLS_LAUNCH((attention_tc_kernel), dim3(n_tiles, n_kv), dim3(THREADS), SMEM_BYTES, stream, P,
+               kmap, vmap, kmap_wide, vmap_wide);
     return launch_status();
 #else
     return MLS_ERR_UNSUPPORTED;

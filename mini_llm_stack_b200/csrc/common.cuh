@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define MLS_F32 0
 #define MLS_BF16 1
@@ -75,3 +76,49 @@ static __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  A kernel started with `launch_chained` may
+// begin while the kernel before it on the stream still runs, as soon as every
+// block of that kernel has called `chain_release` (or has ended).  What it reads
+// of that kernel's results, and everything it writes, comes after `chain_wait`,
+// which returns once all earlier kernels have finished and their writes are
+// visible.  Between the two a kernel may only touch memory that no kernel writes
+// (weights).  Both are no-ops in a kernel that was launched the plain way.
+static __device__ __forceinline__ void chain_release() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+static __device__ __forceinline__ void chain_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// MLS_B200_CHAINED=0 launches every kernel the plain way.
+static inline bool chained_launches() {
+    static const bool on = [] {
+        const char* v = getenv("MLS_B200_CHAINED");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+
+template <typename... Params, typename... Args>
+static inline int launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = chained_launches() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
+// Launch inside a launcher that returns an int: leaves with the error if there is one.
+#define MLS_LAUNCH(kernel, grid, block, smem, stream, ...)                              \
+    do {                                                                                \
+        const int rc_ = launch_chained(kernel, grid, block, smem, stream, __VA_ARGS__); \
+        if (rc_) return rc_;                                                            \
+    } while (0)

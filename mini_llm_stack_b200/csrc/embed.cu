@@ -5,6 +5,8 @@
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ x, int d, int vocab, int* status) {
+    chain_release();
+    chain_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     bool bad = id < 0 || id >= vocab;
@@ -22,10 +24,10 @@ MLS_API int mls_embed(const int* ids, const void* table, int table_dtype, float*
     if (n_tokens <= 0) return 0;
     int threads = d >= 1024 ? 256 : (d >= 256 ? 128 : 64);
     if (table_dtype == MLS_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            ids, (const __nv_bfloat16*)table, x, d, vocab, status);
+        MLS_LAUNCH((embed_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(threads), 0, stream, ids,
+                   (const __nv_bfloat16*)table, x, d, vocab, status);
     else
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            ids, (const float*)table, x, d, vocab, status);
+        MLS_LAUNCH((embed_kernel<float>), dim3(n_tokens), dim3(threads), 0, stream, ids,
+                   (const float*)table, x, d, vocab, status);
     return launch_status();
 }

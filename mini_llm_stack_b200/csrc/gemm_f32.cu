@@ -13,6 +13,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;   // 256 threads
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ out,
                 int M, int N, int K, int ldo) {
+    chain_release();
+    chain_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -66,6 +68,6 @@ MLS_API int mls_gemm_f32(const float* A, const float* W, float* out, int M, int 
                          cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, out, M, N, K, N);
+    MLS_LAUNCH((gemm_f32_kernel), dim3(grid), dim3(256), 0, stream, A, W, out, M, N, K, N);
     return launch_status();
 }

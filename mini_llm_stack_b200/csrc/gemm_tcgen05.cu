@@ -152,6 +152,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
     const int kblocks = (p.k + BK - 1) / BK;
     const int per = (kblocks + p.splits - 1) / p.splits;
 
+    chain_release();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full(s), 1);
@@ -175,6 +176,25 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
         if (lane == 0) {
+            // The weights are nobody's output: the first ring of them is asked for
+            // while the kernel before this one may still run.  The activations, and
+            // all that follows from them, come after chain_wait.
+            const bool w_is_a = p.transposed != 0;
+            int ahead = 0;
+            if ((int)blockIdx.x < tile_count) {
+                const int tile = blockIdx.x;
+                const int mi = tile % m_tiles, rest = tile / m_tiles;
+                const int ni = rest % n_tiles, z = rest / n_tiles;
+                const int kb0 = z * per, n_kb = max(0, min(kblocks, kb0 + per) - kb0);
+                ahead = min(n_kb, STAGES);
+                for (int i = 0; i < ahead; ++i) {
+                    const uint32_t a_dst = base + i * L::STAGE, b_dst = a_dst + L::A_BYTES;
+                    mbar_arrive_expect_tx(full(i), L::A_BYTES + L::B_BYTES);
+                    if (w_is_a) tma_load_2d(a_dst, &amap, (kb0 + i) * BK, mi * BM, full(i));
+                    else tma_load_2d(b_dst, &bmap, (kb0 + i) * BK, ni * BN, full(i));
+                }
+            }
+            chain_wait();
             int g = 0;                                       // k-blocks issued so far
             for (int tile = blockIdx.x; tile < tile_count && !timed_out; tile += gridDim.x) {
                 const int mi = tile % m_tiles, rest = tile / m_tiles;
@@ -182,18 +202,25 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
                 const int kb0 = z * per, n_kb = max(0, min(kblocks, kb0 + per) - kb0);
                 for (int i = 0; i < n_kb; ++i, ++g) {
                     const int slot = g % STAGES;
-                    if (!mbar_wait(empty(slot), ((g / STAGES) & 1) ^ 1)) {
-                        timed_out = true;
-                        break;
-                    }
                     const uint32_t a_dst = base + slot * L::STAGE, b_dst = a_dst + L::A_BYTES;
-                    mbar_arrive_expect_tx(full(slot), L::A_BYTES + L::B_BYTES);
-                    tma_load_2d(a_dst, &amap, (kb0 + i) * BK, mi * BM, full(slot));
-                    tma_load_2d(b_dst, &bmap, (kb0 + i) * BK, ni * BN, full(slot));
+                    const bool begun = g < ahead;            // its weights are on their way
+                    if (!begun) {
+                        if (!mbar_wait(empty(slot), ((g / STAGES) & 1) ^ 1)) {
+                            timed_out = true;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(full(slot), L::A_BYTES + L::B_BYTES);
+                    }
+                    if (!begun || !w_is_a)
+                        tma_load_2d(a_dst, &amap, (kb0 + i) * BK, mi * BM, full(slot));
+                    if (!begun || w_is_a)
+                        tma_load_2d(b_dst, &bmap, (kb0 + i) * BK, ni * BN, full(slot));
                 }
             }
         }
+        chain_wait();
     } else if (warp == 1) {
+        chain_wait();
         // --------------------------------------------------------------- MMA issue
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BN);
@@ -227,6 +254,7 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
         }
     } else {
         // ---------------------------------------------------------------- epilogue
+        chain_wait();
         const int q = warp & 3;                     // this warp's quarter of the 128 lanes
         int it = 0;
         for (int tile = blockIdx.x; tile < tile_count; tile += gridDim.x, ++it) {
@@ -302,6 +330,8 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
 // order the output has ([token][feature] in both orientations).
 __global__ void splitk_sum_kernel(const float* __restrict__ partial, void* __restrict__ out,
                                   int out_f32, int rows, int cols, int splits, int epilogue) {
+    chain_release();
+    chain_wait();
     const size_t n = (size_t)rows * cols;
     const int out_cols = epilogue == 1 ? cols / 2 : cols;
     const size_t total = (size_t)rows * out_cols;
@@ -370,7 +400,8 @@ int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
     const long long tiles = (long long)((p.mm + BM - 1) / BM) * ((p.nn + BN - 1) / BN) * p.splits;
     const long long most = 148LL * ctas_per_sm;
     const int grid = (int)(tiles < most ? tiles : most);
-    gemm_tcgen05_kernel<BN, STAGES><<<grid, THREADS, L::TOTAL, stream>>>(p, amap, bmap);
+    MLS_LAUNCH((gemm_tcgen05_kernel<BN, STAGES>), dim3(grid), dim3(THREADS), L::TOTAL, stream, p,
+               amap, bmap);
     return launch_status();
 }
 }  // namespace
@@ -411,7 +442,8 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
         const size_t total = (size_t)m * p.ld_out;
         int blocks = (int)((total + 255) / 256);
         if (blocks > 148 * 8) blocks = 148 * 8;
-        splitk_sum_kernel<<<blocks, 256, 0, stream>>>(partial, out, out_f32, m, n, splits, epilogue);
+        MLS_LAUNCH((splitk_sum_kernel), dim3(blocks), dim3(256), 0, stream, partial, out, out_f32,
+                   m, n, splits, epilogue);
         return launch_status();
     }
     if (splits != 1) return MLS_ERR_UNSUPPORTED;               // prompts have tiles enough

@@ -41,6 +41,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
                                        int delta_dtype, const void* __restrict__ w, int w_dtype,
                                        float eps, void* __restrict__ h, int h_dtype, int d,
                                        const int* __restrict__ rows) {
+    chain_release();
+    chain_wait();
     __shared__ float scratch[33];
     const int out_row = blockIdx.x;
     const int src_row = rows ? rows[out_row] : out_row;
@@ -91,6 +93,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
                                    int delta_dtype, const void* __restrict__ w, int w_dtype,
                                    float eps, void* __restrict__ h, int h_dtype, int d,
                                    const int* __restrict__ rows) {
+    chain_release();
+    chain_wait();
     __shared__ float scratch[33];
     const int out_row = blockIdx.x;
     const int src_row = rows ? rows[out_row] : out_row;
@@ -127,19 +131,19 @@ MLS_API int mls_add_rmsnorm(float* x, const void* delta, int delta_dtype, const 
         while (threads < 1024 && threads < n4) threads <<= 1;
         const int vec = (n4 + threads - 1) / threads;      // chunks of four per thread: 1..4
         if (vec <= 1)
-            add_rmsnorm_vec_kernel<1><<<n_rows, threads, 0, stream>>>(
-                x, delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+            MLS_LAUNCH((add_rmsnorm_vec_kernel<1>), dim3(n_rows), dim3(threads), 0, stream, x,
+                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
         else if (vec <= 2)
-            add_rmsnorm_vec_kernel<2><<<n_rows, threads, 0, stream>>>(
-                x, delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+            MLS_LAUNCH((add_rmsnorm_vec_kernel<2>), dim3(n_rows), dim3(threads), 0, stream, x,
+                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
         else
-            add_rmsnorm_vec_kernel<4><<<n_rows, threads, 0, stream>>>(
-                x, delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+            MLS_LAUNCH((add_rmsnorm_vec_kernel<4>), dim3(n_rows), dim3(threads), 0, stream, x,
+                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
         return launch_status();
     }
     int threads = 32;
     while (threads < 1024 && threads * 4 < d) threads <<= 1;
-    add_rmsnorm_kernel<<<n_rows, threads, 0, stream>>>(x, delta, delta_dtype, w, w_dtype, eps, h,
-                                                       h_dtype, d, rows);
+    MLS_LAUNCH((add_rmsnorm_kernel), dim3(n_rows), dim3(threads), 0, stream, x, delta, delta_dtype,
+               w, w_dtype, eps, h, h_dtype, d, rows);
     return launch_status();
 }

@@ -19,6 +19,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   T* __restrict__ v_pool, int n_heads, int n_kv, int hd,
                                   int block_size, int max_pos, long long pool_slots, int writes,
                                   int* status) {
+    chain_release();
+    chain_wait();
     const int t = blockIdx.x;
     const int half = hd >> 1;
     int pos = positions[t];
@@ -108,6 +110,8 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
                                       T* __restrict__ v_pool, int n_heads, int n_kv, int hd,
                                       int block_size, int max_pos, long long pool_slots, int writes,
                                       int* status) {
+    chain_release();
+    chain_wait();
     constexpr int N = Vec16<T>::N;
     const int t = blockIdx.x;
     const int half = hd >> 1, cph = half / N;            // chunks per half head
@@ -174,27 +178,28 @@ MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const flo
         int vthreads = 32;
         while (vthreads < 512 && vthreads < units) vthreads <<= 1;
         if (dtype == MLS_BF16)
-            rope_store_vec_kernel<__nv_bfloat16><<<n_tokens, vthreads, 0, stream>>>(
-                (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map, (__nv_bfloat16*)k_pool,
-                (__nv_bfloat16*)v_pool, n_heads, n_kv, hd, block_size, max_pos, pool_slots,
-                writes, status);
+            MLS_LAUNCH((rope_store_vec_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(vthreads), 0,
+                       stream, (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map,
+                       (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_heads, n_kv, hd,
+                       block_size, max_pos, pool_slots, writes, status);
         else
-            rope_store_vec_kernel<float><<<n_tokens, vthreads, 0, stream>>>(
-                (float*)qkv, positions, cos_t, sin_t, slot_map, (float*)k_pool, (float*)v_pool,
-                n_heads, n_kv, hd, block_size, max_pos, pool_slots, writes, status);
+            MLS_LAUNCH((rope_store_vec_kernel<float>), dim3(n_tokens), dim3(vthreads), 0, stream,
+                       (float*)qkv, positions, cos_t, sin_t, slot_map, (float*)k_pool,
+                       (float*)v_pool, n_heads, n_kv, hd, block_size, max_pos, pool_slots, writes,
+                       status);
         return launch_status();
     }
     const int work = (n_heads + n_kv) * hd / 2;
     int threads = 64;
     while (threads < 512 && threads < work) threads <<= 1;
     if (dtype == MLS_BF16)
-        rope_store_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map, (__nv_bfloat16*)k_pool,
-            (__nv_bfloat16*)v_pool, n_heads, n_kv, hd, block_size, max_pos, pool_slots, writes,
-            status);
+        MLS_LAUNCH((rope_store_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(threads), 0, stream,
+                   (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map, (__nv_bfloat16*)k_pool,
+                   (__nv_bfloat16*)v_pool, n_heads, n_kv, hd, block_size, max_pos, pool_slots,
+                   writes, status);
     else
-        rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            (float*)qkv, positions, cos_t, sin_t, slot_map, (float*)k_pool, (float*)v_pool,
-            n_heads, n_kv, hd, block_size, max_pos, pool_slots, writes, status);
+        MLS_LAUNCH((rope_store_kernel<float>), dim3(n_tokens), dim3(threads), 0, stream,
+                   (float*)qkv, positions, cos_t, sin_t, slot_map, (float*)k_pool, (float*)v_pool,
+                   n_heads, n_kv, hd, block_size, max_pos, pool_slots, writes, status);
     return launch_status();
 }

@@ -41,6 +41,8 @@ __device__ __forceinline__ int block_argmax(const float* row, int vocab, float s
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const float* __restrict__ uniform, int* __restrict__ out, int vocab) {
+    chain_release();
+    chain_wait();
     __shared__ float vs[THREADS];
     __shared__ int is[THREADS];
     __shared__ float scratch[33];
@@ -91,6 +93,8 @@ constexpr int CHUNK = 4096;
 __global__ void __launch_bounds__(THREADS)
 argmax_chunks_kernel(const float* __restrict__ logits, float* __restrict__ part_val,
                      int* __restrict__ part_idx, int vocab, int n_chunks) {
+    chain_release();
+    chain_wait();
     __shared__ float vs[THREADS];
     __shared__ int is[THREADS];
     const int begin = blockIdx.y * CHUNK;
@@ -106,6 +110,8 @@ argmax_chunks_kernel(const float* __restrict__ logits, float* __restrict__ part_
 __global__ void argmax_pick_kernel(const float* __restrict__ part_val,
                                    const int* __restrict__ part_idx, int* __restrict__ out,
                                    int n_chunks) {
+    chain_release();
+    chain_wait();
     // one warp a row; chunks are in index order, so the first maximum wins
     const float* v = part_val + (size_t)blockIdx.x * n_chunks;
     const int* ix = part_idx + (size_t)blockIdx.x * n_chunks;
@@ -133,11 +139,13 @@ MLS_API int mls_sample(const float* logits, const float* temperature, const floa
         const int n_chunks = (vocab + CHUNK - 1) / CHUNK;
         float* part_val = scratch;
         int* part_idx = reinterpret_cast<int*>(scratch + (size_t)n_rows * n_chunks);
-        argmax_chunks_kernel<<<dim3(n_rows, n_chunks), THREADS, 0, stream>>>(
-            logits, part_val, part_idx, vocab, n_chunks);
-        argmax_pick_kernel<<<n_rows, 32, 0, stream>>>(part_val, part_idx, out, n_chunks);
+        MLS_LAUNCH((argmax_chunks_kernel), dim3(n_rows, n_chunks), dim3(THREADS), 0, stream, logits,
+                   part_val, part_idx, vocab, n_chunks);
+        MLS_LAUNCH((argmax_pick_kernel), dim3(n_rows), dim3(32), 0, stream, part_val, part_idx, out,
+                   n_chunks);
         return launch_status();
     }
-    sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, temperature, uniform, out, vocab);
+    MLS_LAUNCH((sample_kernel), dim3(n_rows), dim3(THREADS), 0, stream, logits, temperature,
+               uniform, out, vocab);
     return launch_status();
 }

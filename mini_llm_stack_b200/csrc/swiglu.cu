@@ -9,6 +9,8 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f 
 // 16 bytes per thread and operand: I must be a multiple of 8 (bfloat16) or 4 (float32).
 __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
                                      __nv_bfloat16* __restrict__ out, int inter) {
+    chain_release();
+    chain_wait();
     const size_t t = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;       // chunk of 8
     if (c * 8 >= inter) return;
@@ -29,6 +31,8 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu,
 
 __global__ void swiglu_f32x4_kernel(const float* __restrict__ gu, float* __restrict__ out,
                                     int inter) {
+    chain_release();
+    chain_wait();
     const size_t t = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;       // chunk of 4
     if (c * 4 >= inter) return;
@@ -45,6 +49,8 @@ __global__ void swiglu_f32x4_kernel(const float* __restrict__ gu, float* __restr
 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+    chain_release();
+    chain_wait();
     const size_t t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
@@ -60,18 +66,20 @@ MLS_API int mls_swiglu(const void* gu, void* out, int dtype, int n_tokens, int i
     const int threads = 256;
     if (dtype == MLS_BF16 && inter % 8 == 0) {
         dim3 grid((inter / 8 + threads - 1) / threads, n_tokens);
-        swiglu_bf16x8_kernel<<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gu,
-                                                           (__nv_bfloat16*)out, inter);
+        MLS_LAUNCH((swiglu_bf16x8_kernel), dim3(grid), dim3(threads), 0, stream,
+                   (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
     } else if (dtype == MLS_F32 && inter % 4 == 0) {
         dim3 grid((inter / 4 + threads - 1) / threads, n_tokens);
-        swiglu_f32x4_kernel<<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, inter);
+        MLS_LAUNCH((swiglu_f32x4_kernel), dim3(grid), dim3(threads), 0, stream, (const float*)gu,
+                   (float*)out, inter);
     } else {
         dim3 grid((inter + threads - 1) / threads, n_tokens);
         if (dtype == MLS_BF16)
-            swiglu_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
+            MLS_LAUNCH((swiglu_kernel<__nv_bfloat16>), dim3(grid), dim3(threads), 0, stream,
+                       (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
         else
-            swiglu_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, inter);
+            MLS_LAUNCH((swiglu_kernel<float>), dim3(grid), dim3(threads), 0, stream,
+                       (const float*)gu, (float*)out, inter);
     }
     return launch_status();
 }

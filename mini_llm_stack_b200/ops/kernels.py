@@ -198,9 +198,13 @@ class Ops:
         between it and the library is ``MLS_B200_GEMM`` (tcgen05 | cublas | auto)."""
         if self.gemm_impl == "cublas" or k % 8 != 0:
             return False
-        # auto: plain products go to the library (as the reference's nn.Linear does);
-        # the tcgen05 kernel runs where it fuses work (``linear_swiglu``)
-        return self.gemm_impl == "tcgen05"
+        if self.gemm_impl == "tcgen05":
+            return True
+        # auto: a few rows (decoding) go to the tcgen05 kernel, which asks for its
+        # first weights while the kernel before it still runs; more rows go to the
+        # library (as the reference's nn.Linear does) unless the kernel fuses work
+        # (``linear_swiglu``)
+        return m <= 32
 
     def _gemm_bf16(self, a, w, out, m: int, n: int, k: int, epilogue: int = 0) -> None:
         if self._gemm is None:

@@ -133,6 +133,18 @@ def _run(cmd: list, what: str) -> None:
         raise KernelBuildError(f"compiling {what} failed:\n{' '.join(cmd)}\n{out}")
 
 
+def _drop_stale(fresh: Path) -> None:
+    """Remove libraries of the same module and defines built from other sources."""
+    prefix = fresh.name[:-len("0123456789ab.so")]
+    for other in fresh.parent.glob(prefix + "*.so"):
+        rest = other.name[len(prefix):-len(".so")]
+        if other != fresh and len(rest) == 12 and all(c in "0123456789abcdef" for c in rest):
+            try:
+                other.unlink()
+            except OSError:
+                pass
+
+
 def build(name: str, defines: dict | None = None, verbose: bool = True) -> Path:
     """Compile module ``name`` if its library does not exist yet; return its path."""
     defines = defines or {}
@@ -161,6 +173,7 @@ def build(name: str, defines: dict | None = None, verbose: bool = True) -> Path:
         _run([nvcc, "-shared", *[str(o) for o in objs], "-o", str(tmp),
               "-lcudart"], f"link {name}")
         os.replace(tmp, out)
+        _drop_stale(out)
     finally:
         for o in objs:
             try:
