@@ -302,7 +302,7 @@ def main() -> int:
         runner.step(e)
         runner.release("prefill")
 
-    prefill_ms, _ = timed(prefill_once, 3, 5)
+    prefill_ms, _ = timed(prefill_once, 3, 8)
     pf = prefill_flops(raw, args.layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                "ms": round(prefill_ms, 3),

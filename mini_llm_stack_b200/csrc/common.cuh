@@ -91,13 +91,21 @@ static __device__ __forceinline__ void chain_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// MLS_B200_CHAINED=0 launches every kernel the plain way.
+// Whether launches are chained: off for good with MLS_B200_CHAINED=0 in the
+// environment, else as the host last said through mls_set_chained (one switch per
+// shared library).  A chained kernel that waits keeps its warps resident beside the
+// kernel before it; under long kernels (a prompt's matrix products) that costs more
+// than the early start gains, so the host chains the steps of few tokens only.
+inline int g_chained = 1;
 static inline bool chained_launches() {
-    static const bool on = [] {
+    static const bool allowed = [] {
         const char* v = getenv("MLS_B200_CHAINED");
         return !(v && v[0] == '0');
     }();
-    return on;
+    return allowed && g_chained != 0;
+}
+extern "C" __attribute__((visibility("default"), used)) inline void mls_set_chained(int on) {
+    g_chained = on;
 }
 
 template <typename... Params, typename... Args>

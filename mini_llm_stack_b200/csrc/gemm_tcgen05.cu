@@ -409,13 +409,15 @@ int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
 // out[M, N] = act[M, K] * w[N, K]^T, bfloat16 operands, out bfloat16 or float32.
 // swap: 1 = the weights take the 128-row side (decoding, M <= 64).  splits > 1 cuts K
 // (weight-major orientation only) and needs `partial`, float32 scratch of
-// splits * M * N, which a second kernel adds up.  epilogue 1: the weight rows alternate between
+// splits * M * N, which a second kernel adds up (with out == nullptr the parts are left
+// to the caller, [part][M][N]).  epilogue 1: the weight rows alternate between
 // 16 gate rows and the 16 matching up rows, and out[M, N / 2] = silu(gate) * up.
 MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32, int m, int n,
                           int k, int swap, int splits, int epilogue, float* partial, int* status,
                           cudaStream_t stream) {
     if (m <= 0 || n <= 0) return 0;
     if (k % 8 != 0 || k <= 0) return MLS_ERR_UNSUPPORTED;      // rows must be 16-byte multiples
+    if (out == nullptr && (splits < 2 || !swap || epilogue != 0)) return MLS_ERR_UNSUPPORTED;
     if (splits < 1 || (splits > 1 && partial == nullptr))
         return MLS_ERR_UNSUPPORTED;
     if (epilogue == 1 && n % 32 != 0) return MLS_ERR_UNSUPPORTED;
@@ -438,7 +440,7 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
         if (m <= 16) rc = launch<16, 6>(p, w, act, 2, stream);
         else if (m <= 32) rc = launch<32, 5>(p, w, act, 2, stream);
         else rc = launch<64, 4>(p, w, act, 2, stream);
-        if (rc || splits == 1) return rc;
+        if (rc || splits == 1 || out == nullptr) return rc;
         const size_t total = (size_t)m * p.ld_out;
         int blocks = (int)((total + 255) / 256);
         if (blocks > 148 * 8) blocks = 148 * 8;

@@ -9,6 +9,10 @@
 // rows != nullptr: for i < n_rows: v = x[rows[i]] + delta[rows[i]], h[i] = norm(v);
 //                  x is not modified.
 //
+// delta_parts > 1: delta is that many float32 slices, part_stride elements apart (the
+// parts of a matrix product cut along K); their sum, taken in the order of the
+// slices, is the delta.
+//
 // The sum of squares is taken in an order that depends on the row's width only,
 // so a row's result does not depend on the batch it is in.
 #include "common.cuh"
@@ -35,12 +39,32 @@ __device__ __forceinline__ void store4(void* base, size_t i, int dtype, float4 v
     }
 }
 
+__device__ __forceinline__ float4 load_delta4(const void* delta, size_t i, int dtype, int parts,
+                                              size_t stride) {
+    float4 s = load4(delta, i, dtype);
+    for (int k = 1; k < parts; ++k) {
+        const float4 b = load4(delta, i + k * stride, dtype);
+        s.x += b.x;
+        s.y += b.y;
+        s.z += b.z;
+        s.w += b.w;
+    }
+    return s;
+}
+__device__ __forceinline__ float load_delta(const void* delta, size_t i, int dtype, int parts,
+                                            size_t stride) {
+    float s = load_as_float(delta, i, dtype);
+    for (int k = 1; k < parts; ++k) s += load_as_float(delta, i + k * stride, dtype);
+    return s;
+}
+
 // d a multiple of 4 and d / 4 <= blockDim.x * VEC: a row lives in registers.
 template <int VEC>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __restrict__ delta,
                                        int delta_dtype, const void* __restrict__ w, int w_dtype,
                                        float eps, void* __restrict__ h, int h_dtype, int d,
-                                       const int* __restrict__ rows) {
+                                       const int* __restrict__ rows, int delta_parts,
+                                       size_t part_stride) {
     chain_release();
     chain_wait();
     __shared__ float scratch[33];
@@ -57,7 +81,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
         if (c < n4) {
             float4 a = *reinterpret_cast<const float4*>(x + xoff + 4 * c);
             if (delta) {
-                const float4 b = load4(delta, xoff + 4 * c, delta_dtype);
+                const float4 b = load_delta4(delta, xoff + 4 * c, delta_dtype, delta_parts,
+                                             part_stride);
                 a.x += b.x;
                 a.y += b.y;
                 a.z += b.z;
@@ -92,7 +117,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta,
                                    int delta_dtype, const void* __restrict__ w, int w_dtype,
                                    float eps, void* __restrict__ h, int h_dtype, int d,
-                                   const int* __restrict__ rows) {
+                                   const int* __restrict__ rows, int delta_parts,
+                                   size_t part_stride) {
     chain_release();
     chain_wait();
     __shared__ float scratch[33];
@@ -105,7 +131,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
     float ss = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = xr[i];
-        if (delta) v += load_as_float(delta, doff + i, delta_dtype);
+        if (delta) v += load_delta(delta, doff + i, delta_dtype, delta_parts, part_stride);
         if (in_place && delta) xr[i] = v;
         ss += v * v;
     }
@@ -114,7 +140,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
     const size_t hoff = (size_t)out_row * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = xr[i];
-        if (!in_place && delta) v += load_as_float(delta, doff + i, delta_dtype);
+        if (!in_place && delta)
+            v += load_delta(delta, doff + i, delta_dtype, delta_parts, part_stride);
         float y = (v * r) * load_as_float(w, i, w_dtype);
         store_from_float(h, hoff + i, h_dtype, y);
     }
@@ -123,8 +150,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict
 
 MLS_API int mls_add_rmsnorm(float* x, const void* delta, int delta_dtype, const void* w,
                             int w_dtype, float eps, void* h, int h_dtype, int n_rows, int d,
-                            const int* rows, cudaStream_t stream) {
+                            const int* rows, int delta_parts, long long part_stride,
+                            cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (delta_parts < 1 || (delta_parts > 1 && (delta_dtype != MLS_F32 || part_stride % 4 != 0)))
+        return MLS_ERR_UNSUPPORTED;
+    const size_t stride = (size_t)part_stride;
     if (d % 4 == 0 && d / 4 <= 1024 * 4) {
         const int n4 = d / 4;
         int threads = 32;
@@ -132,18 +163,21 @@ MLS_API int mls_add_rmsnorm(float* x, const void* delta, int delta_dtype, const 
         const int vec = (n4 + threads - 1) / threads;      // chunks of four per thread: 1..4
         if (vec <= 1)
             MLS_LAUNCH((add_rmsnorm_vec_kernel<1>), dim3(n_rows), dim3(threads), 0, stream, x,
-                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows, delta_parts,
+                       stride);
         else if (vec <= 2)
             MLS_LAUNCH((add_rmsnorm_vec_kernel<2>), dim3(n_rows), dim3(threads), 0, stream, x,
-                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows, delta_parts,
+                       stride);
         else
             MLS_LAUNCH((add_rmsnorm_vec_kernel<4>), dim3(n_rows), dim3(threads), 0, stream, x,
-                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows);
+                       delta, delta_dtype, w, w_dtype, eps, h, h_dtype, d, rows, delta_parts,
+                       stride);
         return launch_status();
     }
     int threads = 32;
     while (threads < 1024 && threads * 4 < d) threads <<= 1;
     MLS_LAUNCH((add_rmsnorm_kernel), dim3(n_rows), dim3(threads), 0, stream, x, delta, delta_dtype,
-               w, w_dtype, eps, h, h_dtype, d, rows);
+               w, w_dtype, eps, h, h_dtype, d, rows, delta_parts, stride);
     return launch_status();
 }

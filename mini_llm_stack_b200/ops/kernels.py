@@ -62,6 +62,46 @@ def _decl(lib, name, argtypes):
     return fn
 
 
+class SplitParts:
+    """A matrix product left as the parts of a cut along K: float32 [parts, M, N].
+
+    Their sum, taken in the order of the slices, is the product.  ``add_rmsnorm``
+    adds them up while it reads the residual row anyway, which saves the kernel
+    that would do nothing else.  The parts live in one scratch buffer of the
+    kernels' owner: they are read (or given up) before the next product that
+    wants the buffer, which otherwise takes the ordinary way.
+    """
+
+    __slots__ = ("parts", "_ops")
+
+    def __init__(self, parts, ops):
+        self.parts = parts
+        self._ops = ops
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    def release(self) -> None:
+        if self._ops is not None:
+            self._ops._delta_parts_busy = False
+            self._ops = None
+
+    def float(self):
+        """The product as a float32 tensor of its own."""
+        out = self.parts[0].clone()
+        for k in range(1, self.parts.shape[0]):
+            out += self.parts[k]
+        self.release()
+        return out
+
+    def clone(self):
+        return self.float()
+
+    def to(self, dtype):
+        return self.float().to(dtype)
+
+
 class Ops:
     """The kernels, bound to one device.  Fails at construction without a GPU."""
 
@@ -72,10 +112,12 @@ class Ops:
                 "this engine runs on a CUDA device only (sm_100a kernels); "
                 f"device {device!r} is not one and there is no CPU path")
         self.act_dtype = act_dtype
-        core = library.load("core")
+        self._libs: list = []                    # every kernel library in use
+        self._chained = True                     # what the libraries were last told
+        core = self._load("core")
         self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _P, _P])
         self._add_rmsnorm = _decl(core, "mls_add_rmsnorm",
-                                  [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _P])
+                                  [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _I, _LL, _P])
         self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _P, _P, _I, _I, _I, _P])
         self._rope_store = _decl(core, "mls_rope_store",
                                  [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
@@ -91,6 +133,7 @@ class Ops:
         self._attention_shapes: set = set()      # (kv heads, group size) of the mixers
         self._scratch: dict = {}
         self._gemm = None
+        self._delta_parts_busy = False
         self.attention_impl = os.environ.get("MLS_B200_ATTENTION", "auto")
         self.gemm_impl = os.environ.get("MLS_B200_GEMM", "auto")
         self.generation = 0          # grows whenever a buffer kernels were given moves
@@ -98,6 +141,26 @@ class Ops:
         self.library_launches = 0    # plain matrix products handed to the library
 
     # ------------------------------------------------------------------ helpers
+    def _load(self, name: str, defines: dict | None = None):
+        lib = library.load(name, defines)
+        lib.mls_set_chained.argtypes = [_I]
+        lib.mls_set_chained.restype = None
+        lib.mls_set_chained(1 if self._chained else 0)
+        self._libs.append(lib)
+        return lib
+
+    CHAINED_UP_TO = 256      # tokens of a step whose kernels start under their predecessors
+
+    def begin_step(self, n_tokens: int) -> None:
+        """Tell the kernel libraries how to launch this step's kernels: chained
+        (each may start, and fetch what no kernel writes, while the one before it
+        still runs) pays when kernels are short, plain when they are long."""
+        on = n_tokens <= self.CHAINED_UP_TO
+        if on != self._chained:
+            self._chained = on
+            for lib in self._libs:
+                lib.mls_set_chained(1 if on else 0)
+
     def scratch(self, tag: str, n_floats: int):
         """Float32 scratch memory that lives as long as the kernels' owner."""
         buf = self._scratch.get(tag)
@@ -131,32 +194,44 @@ class Ops:
         _check(self._embed(_ptr(token_ids), _ptr(table), _code(table.dtype), _ptr(x), t, d,
                            vocab, _ptr(self.status), self._stream()), "embed")
 
+    def _delta_args(self, delta, t: int, d: int, what: str):
+        """(pointer, type code, parts, part stride) of a pending residual delta."""
+        if delta is None:
+            return None, 0, 1, 0
+        if isinstance(delta, SplitParts):
+            parts = delta.parts
+            _need(parts.shape[1:] == (t, d) and parts.is_contiguous()
+                  and parts.dtype == torch.float32, f"{what}: bad delta parts")
+            return parts.data_ptr(), 0, parts.shape[0], t * d
+        _need(delta.shape == (t, d) and delta.is_contiguous(), f"{what}: bad delta")
+        return delta.data_ptr(), _code(delta.dtype), 1, 0
+
     def add_rmsnorm(self, x, delta, weight, eps: float, h) -> None:
+        """``x += delta`` (a tensor, ``SplitParts`` or None), ``h = rmsnorm(x) * weight``."""
         t, d = x.shape
         _need(x.dtype == torch.float32 and x.is_contiguous(), "add_rmsnorm: x must be float32")
         _need(h.shape == (t, d) and h.is_contiguous(), "add_rmsnorm: bad output")
         _need(weight.shape == (d,), "add_rmsnorm: bad weight")
-        if delta is not None:
-            _need(delta.shape == (t, d) and delta.is_contiguous(), "add_rmsnorm: bad delta")
+        dp, dcode, parts, stride = self._delta_args(delta, t, d, "add_rmsnorm")
         self.launches += 1
-        _check(self._add_rmsnorm(_ptr(x), _ptr(delta),
-                                 _code(delta.dtype) if delta is not None else 0,
-                                 _ptr(weight), _code(weight.dtype), float(eps), _ptr(h),
-                                 _code(h.dtype), t, d, None, self._stream()), "add_rmsnorm")
+        _check(self._add_rmsnorm(_ptr(x), dp, dcode, _ptr(weight), _code(weight.dtype),
+                                 float(eps), _ptr(h), _code(h.dtype), t, d, None, parts, stride,
+                                 self._stream()), "add_rmsnorm")
+        if isinstance(delta, SplitParts):
+            delta.release()
 
     def gather_add_rmsnorm(self, x, delta, rows, n_rows: int, weight, eps: float, h) -> None:
         t, d = x.shape
         _need(x.dtype == torch.float32 and x.is_contiguous(), "gather_add_rmsnorm: bad x")
         _need(h.shape == (n_rows, d) and h.is_contiguous(), "gather_add_rmsnorm: bad output")
         _need(rows.dtype == torch.int32 and rows.numel() >= n_rows, "gather_add_rmsnorm: rows")
-        if delta is not None:
-            _need(delta.shape == (t, d) and delta.is_contiguous(), "gather_add_rmsnorm: delta")
+        dp, dcode, parts, stride = self._delta_args(delta, t, d, "gather_add_rmsnorm")
         self.launches += 1
-        _check(self._add_rmsnorm(_ptr(x), _ptr(delta),
-                                 _code(delta.dtype) if delta is not None else 0,
-                                 _ptr(weight), _code(weight.dtype), float(eps), _ptr(h),
-                                 _code(h.dtype), n_rows, d, _ptr(rows), self._stream()),
-               "gather_add_rmsnorm")
+        _check(self._add_rmsnorm(_ptr(x), dp, dcode, _ptr(weight), _code(weight.dtype),
+                                 float(eps), _ptr(h), _code(h.dtype), n_rows, d, _ptr(rows),
+                                 parts, stride, self._stream()), "gather_add_rmsnorm")
+        if isinstance(delta, SplitParts):
+            delta.release()
 
     def prepare_weight(self, w):
         """A matrix [out, in] made ready for ``linear`` (contiguous, on device)."""
@@ -206,27 +281,56 @@ class Ops:
         # (``linear_swiglu``)
         return m <= 32
 
-    def _gemm_bf16(self, a, w, out, m: int, n: int, k: int, epilogue: int = 0) -> None:
+    def _gemm_splits(self, m: int, n: int, k: int) -> int:
+        """Parts along K for the weight-major orientation (M <= 64): the weights are
+        read once; every tile x part is a CTA, and two CTAs fit an SM: as many CTAs
+        as fit at the same time, at least 256 of K each."""
+        tiles = (n + 127) // 128
+        kblocks = (k + 63) // 64
+        splits = max(1, min(kblocks // 4, (2 * 148) // tiles))
+        per = -(-kblocks // splits)
+        return -(-kblocks // per)
+
+    def _gemm_bf16(self, a, w, out, m: int, n: int, k: int, epilogue: int = 0,
+                   leave_parts: bool = False):
+        """The tcgen05 product.  ``leave_parts``: the K-parts are not added up but
+        returned as ``SplitParts`` (the caller has checked that there are several)."""
         if self._gemm is None:
-            lib = library.load("gemm")
+            lib = self._load("gemm")
             self._gemm = _decl(lib, "mls_gemm_bf16",
                                [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P])
         swap = 1 if m <= 64 else 0
         splits, partial = 1, None
         if swap:
-            # the weights are read once; every tile x split is a CTA, and two CTAs
-            # fit an SM: as many CTAs as fit at the same time, at least 256 of K each
-            tiles = (n + 127) // 128
-            kblocks = (k + 63) // 64
-            splits = max(1, min(kblocks // 4, (2 * 148) // tiles))
-            per = -(-kblocks // splits)
-            splits = -(-kblocks // per)
+            splits = self._gemm_splits(m, n, k)
             if splits > 1:
-                partial = self.scratch("gemm_partials", splits * m * n)
-        self.launches += 2 if splits > 1 else 1
-        _check(self._gemm(_ptr(a), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                tag = "gemm_delta_parts" if leave_parts else "gemm_partials"
+                partial = self.scratch(tag, splits * m * n)
+        _need(not leave_parts or splits > 1, "gemm_bf16: no parts to leave")
+        self.launches += 2 if splits > 1 and not leave_parts else 1
+        out_f32 = 1 if (out is not None and out.dtype == torch.float32) else 0
+        _check(self._gemm(_ptr(a), _ptr(w), None if leave_parts else _ptr(out), out_f32,
                           m, n, k, swap, splits, epilogue, _ptr(partial), _ptr(self.status),
                           self._stream()), "gemm_bf16")
+        if leave_parts:
+            self._delta_parts_busy = True
+            return SplitParts(partial[:splits * m * n].view(splits, m, n), self)
+        return None
+
+    def linear_delta(self, a, w, out):
+        """A product whose result is only ever added to the residual stream: returns
+        ``out``, filled, or the product's K-parts (``SplitParts``) for the next
+        ``add_rmsnorm`` to add up, with ``out`` untouched."""
+        m, k = a.shape
+        n = w.shape[0]
+        if (0 < m <= 64 and n % 4 == 0 and w.dtype == torch.bfloat16
+                and not self._delta_parts_busy
+                and w.shape == (n, k) and a.is_contiguous() and w.is_contiguous()
+                and self._use_own_gemm(m, n, k) and self._gemm_splits(m, n, k) > 1):
+            a16 = a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
+            return self._gemm_bf16(a16, w, None, m, n, k, leave_parts=True)
+        self.linear(a, w, out)
+        return out
 
     def can_fuse_swiglu(self, d_model: int, inter: int) -> bool:
         """Whether gate-up projection and SwiGLU can run as one kernel."""
@@ -278,7 +382,7 @@ class Ops:
         if n_kv:
             self._attention_shapes.add((n_kv, n_heads // n_kv))
         if self.act_dtype == torch.bfloat16 and hd not in self._attention_libs:
-            lib = library.load("attention", {"MLS_HEAD_DIM": int(hd)})
+            lib = self._load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I,
                         _P, _P, _LL, _P, _I, _P])

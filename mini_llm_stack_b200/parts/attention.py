@@ -63,5 +63,4 @@ class GroupedQueryAttention(Mixer):
         rt.ops.paged_attention(qkv, o, cache, step, self.n_heads, self.n_kv_heads,
                                hd, self.scale, self.window or 0)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
-        rt.ops.linear(o, self.wo, delta)
-        return delta
+        return rt.ops.linear_delta(o, self.wo, delta)

@@ -133,21 +133,29 @@ class ResidualStream:
     """The residual sum, kept in float32, with one pending addend.
 
     ``push(delta)`` defers an addition; the next norm adds it while it reads the
-    row anyway (the reference adds eagerly: train/model.py:212-216).
+    row anyway (the reference adds eagerly: train/model.py:212-216).  A delta is a
+    tensor [T, d_model] or the kernels' ``SplitParts`` (a product left as the parts
+    of a cut along K, which ``add_rmsnorm`` adds up; ``.float()`` gives the tensor).
     """
 
     def __init__(self, x: torch.Tensor):
         self.x = x                   # [T, d_model] float32
-        self.pending: Optional[torch.Tensor] = None
+        self.pending = None
 
-    def push(self, delta: torch.Tensor) -> None:
+    def push(self, delta) -> None:
         if self.pending is not None:
             raise RuntimeError("a delta is already pending on the residual stream")
         self.pending = delta
 
-    def take_pending(self) -> Optional[torch.Tensor]:
+    def take_pending(self):
         p, self.pending = self.pending, None
         return p
+
+    def drop_pending(self) -> None:
+        """Forget the pending delta (the rows it belongs to are not wanted)."""
+        p = self.take_pending()
+        if hasattr(p, "release"):
+            p.release()
 
 
 class Part:

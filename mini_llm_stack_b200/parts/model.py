@@ -130,6 +130,7 @@ class ComposedModel:
     # ------------------------------------------------------------------ forward
     def forward(self, step: StepContext, handles: list):
         """Run the step's tokens; float32 logits [n_out, vocab] at ``out_rows``."""
+        self.runtime.ops.begin_step(step.n_tokens)
         stream = ResidualStream(self.embedding.forward(step))
         none = CacheHandle()
         for call in self.calls:
@@ -140,7 +141,7 @@ class ComposedModel:
                     handle = handle.reader()
             self.blocks[call.layer].forward(stream, step, handle)
         if step.n_out == 0:
-            stream.take_pending()
+            stream.drop_pending()
             return None
         h = self.final_norm.forward(stream, rows=step.out_rows, n_rows=step.n_out)
         return self.head.forward(h, step.n_out)

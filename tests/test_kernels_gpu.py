@@ -134,6 +134,44 @@ def test_linear_bf16(rts, m, n, k, out_dtype, impl):
     assert (out.float() - want).abs().max().item() <= tol * scale + 1e-6
 
 
+@pytest.mark.parametrize("m, n, k", [(1, 4096, 14336), (8, 4096, 4096), (33, 1000, 4104), (64, 96, 2048)])
+def test_product_left_as_parts_is_summed_by_the_next_norm(rts, m, n, k):
+    """A product that only feeds the residual stream keeps its K-parts; add_rmsnorm
+    adds them up, for all rows and for chosen rows, and the buffer is lent once."""
+    from mini_llm_stack_b200.ops.kernels import SplitParts
+    ops = rts[torch.bfloat16].ops
+    a, w = rand((m, k), torch.bfloat16, 21), rand((n, k), torch.bfloat16, 22, 0.05)
+    wp = ops.prepare_weight(w)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_impl = "tcgen05"
+    try:
+        parts = ops.linear_delta(a, wp, out)
+        assert isinstance(parts, SplitParts) and parts.shape == (m, n)
+        again = ops.linear_delta(a, wp, out)              # the buffer is taken: the ordinary way
+        assert again is out
+    finally:
+        ops.gemm_impl = "auto"
+    ops.check_status()
+    want = a.float() @ w.float().t()
+    scale = want.abs().max().item()
+    tol = max(1e-5, 4 * math.sqrt(k) * 2.0 ** -24)
+    x = rand((m, n), torch.float32, 23, 2.0)
+    g = 1 + rand((n,), torch.bfloat16, 24, 0.1)
+    rows = torch.tensor([m - 1, 0], dtype=torch.int32, device=DEV)
+    hg = torch.empty((2, n), dtype=torch.bfloat16, device=DEV)
+    xx = x.clone()
+    ops.gather_add_rmsnorm(xx, SplitParts(parts.parts, None), rows, 2, g, 1e-5, hg)
+    assert torch.equal(xx, x)                             # chosen rows leave the stream alone
+    h = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(xx, parts, g, 1e-5, h)
+    assert (xx - (x + want)).abs().max().item() <= tol * scale + 1e-6
+    want_h = P.plain_rmsnorm((x + want).cpu(), g.cpu(), 1e-5)
+    assert torch.allclose(h.float().cpu(), want_h, rtol=8e-3, atol=8e-3)
+    assert torch.equal(hg[0], h[m - 1]) and torch.equal(hg[1], h[0])
+    assert not ops._delta_parts_busy                      # given back by the norm
+    assert torch.allclose(out.float(), want, rtol=1e-2, atol=5e-3 * scale)   # the ordinary way's result
+
+
 @pytest.mark.parametrize("m, inter, k", [(1, 14336, 4096), (8, 176, 64), (64, 256, 96), (33, 4096, 4096),
                                           (300, 272, 200), (2048, 1024, 512), (129, 14336, 1024)])
 def test_gate_up_projection_with_swiglu_epilogue(rts, m, inter, k):
