@@ -75,6 +75,62 @@ static __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 
     return scratch[32];
 }
 
+// Four consecutive float32 values at `at`, summed over the n_parts slices of a
+// matrix product that was cut along K (slices `stride` elements apart), in the
+// order of the slices.  The loads of up to AT_ONCE slices are under way together.
+template <int AT_ONCE = 8>
+static __device__ __forceinline__ float4 sum_parts4(const float* __restrict__ base, size_t at,
+                                                    int n_parts, size_t stride) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < n_parts; k0 += AT_ONCE) {
+        float4 b[AT_ONCE];
+#pragma unroll
+        for (int j = 0; j < AT_ONCE; ++j)
+            if (k0 + j < n_parts)
+                b[j] = *reinterpret_cast<const float4*>(base + at + (size_t)(k0 + j) * stride);
+#pragma unroll
+        for (int j = 0; j < AT_ONCE; ++j)
+            if (k0 + j < n_parts) {
+                s.x += b[j].x;
+                s.y += b[j].y;
+                s.z += b[j].z;
+                s.w += b[j].w;
+            }
+    }
+    return s;
+}
+
+// The same at M places at once: all their loads are under way together.
+template <int M, int AT_ONCE>
+static __device__ __forceinline__ void sum_parts4_of(const float* __restrict__ base,
+                                                     const size_t (&at)[M], int n_parts,
+                                                     size_t stride, float4 (&out)[M]) {
+#pragma unroll
+    for (int m = 0; m < M; ++m) out[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k0 = 0; k0 < n_parts; k0 += AT_ONCE) {
+        float4 b[M][AT_ONCE];
+#pragma unroll
+        for (int j = 0; j < AT_ONCE; ++j)
+            if (k0 + j < n_parts) {
+#pragma unroll
+                for (int m = 0; m < M; ++m)
+                    b[m][j] = *reinterpret_cast<const float4*>(base + at[m] +
+                                                               (size_t)(k0 + j) * stride);
+            }
+#pragma unroll
+        for (int j = 0; j < AT_ONCE; ++j)
+            if (k0 + j < n_parts) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    out[m].x += b[m][j].x;
+                    out[m].y += b[m][j].y;
+                    out[m].z += b[m][j].z;
+                    out[m].w += b[m][j].w;
+                }
+            }
+    }
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch.  A kernel started with `launch_chained` may

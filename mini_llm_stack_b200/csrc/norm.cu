@@ -41,15 +41,8 @@ __device__ __forceinline__ void store4(void* base, size_t i, int dtype, float4 v
 
 __device__ __forceinline__ float4 load_delta4(const void* delta, size_t i, int dtype, int parts,
                                               size_t stride) {
-    float4 s = load4(delta, i, dtype);
-    for (int k = 1; k < parts; ++k) {
-        const float4 b = load4(delta, i + k * stride, dtype);
-        s.x += b.x;
-        s.y += b.y;
-        s.z += b.z;
-        s.w += b.w;
-    }
-    return s;
+    if (parts > 1) return sum_parts4<4>((const float*)delta, i, parts, stride);
+    return load4(delta, i, dtype);
 }
 __device__ __forceinline__ float load_delta(const void* delta, size_t i, int dtype, int parts,
                                             size_t stride) {
@@ -60,19 +53,25 @@ __device__ __forceinline__ float load_delta(const void* delta, size_t i, int dty
 
 // d a multiple of 4 and d / 4 <= blockDim.x * VEC: a row lives in registers.
 template <int VEC>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __restrict__ delta,
+__global__ void __launch_bounds__(1024) add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __restrict__ delta,
                                        int delta_dtype, const void* __restrict__ w, int w_dtype,
                                        float eps, void* __restrict__ h, int h_dtype, int d,
                                        const int* __restrict__ rows, int delta_parts,
                                        size_t part_stride) {
     chain_release();
-    chain_wait();
     __shared__ float scratch[33];
+    const int n4 = d >> 2;
+    float4 ww[VEC];                       // the weight is nobody's output: read before the wait
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < n4) ww[k] = load4(w, 4 * c, w_dtype);
+    }
+    chain_wait();
     const int out_row = blockIdx.x;
     const int src_row = rows ? rows[out_row] : out_row;
     const size_t xoff = (size_t)src_row * d;
     const bool in_place = rows == nullptr;
-    const int n4 = d >> 2;
     float4 v[VEC];
     float ss = 0.f;
 #pragma unroll
@@ -103,18 +102,17 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const void* __rest
     for (int k = 0; k < VEC; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
         if (c < n4) {
-            const float4 ww = load4(w, 4 * c, w_dtype);
             float4 y;
-            y.x = (v[k].x * r) * ww.x;
-            y.y = (v[k].y * r) * ww.y;
-            y.z = (v[k].z * r) * ww.z;
-            y.w = (v[k].w * r) * ww.w;
+            y.x = (v[k].x * r) * ww[k].x;
+            y.y = (v[k].y * r) * ww[k].y;
+            y.z = (v[k].z * r) * ww[k].z;
+            y.w = (v[k].w * r) * ww[k].w;
             store4(h, hoff + 4 * c, h_dtype, y);
         }
     }
 }
 
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta,
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta,
                                    int delta_dtype, const void* __restrict__ w, int w_dtype,
                                    float eps, void* __restrict__ h, int h_dtype, int d,
                                    const int* __restrict__ rows, int delta_parts,

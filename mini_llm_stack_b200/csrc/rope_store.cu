@@ -111,23 +111,25 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
                                       int block_size, int max_pos, long long pool_slots, int writes,
                                       int* status) {
     chain_release();
-    chain_wait();
     constexpr int N = Vec16<T>::N;
     const int t = blockIdx.x;
     const int half = hd >> 1, cph = half / N;            // chunks per half head
+    // positions and slots were copied before the step's first kernel began
     int pos = positions[t];
-    if (pos < 0 || pos >= max_pos) {
-        if (threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_POSITION);
-        pos = pos < 0 ? 0 : max_pos - 1;
-    }
+    const bool bad_pos = pos < 0 || pos >= max_pos;
+    if (bad_pos) pos = pos < 0 ? 0 : max_pos - 1;
     const float* cr = cos_t + (size_t)pos * half;
     const float* sr = sin_t + (size_t)pos * half;
     T* row = qkv + (size_t)t * (n_heads + 2 * n_kv) * hd;
     long long slot = writes ? (long long)slot_map[t] : 0;
     const bool slot_ok = slot >= 0 && slot < pool_slots;
-    if (writes && !slot_ok && threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_SLOT);
     const long long page = slot / block_size, off = slot % block_size;
     const long long n_pages = pool_slots / block_size;
+    chain_wait();
+    if (threadIdx.x == 0 && status) {
+        if (bad_pos) atomicOr(status, MLS_STATUS_BAD_POSITION);
+        if (writes && !slot_ok) atomicOr(status, MLS_STATUS_BAD_SLOT);
+    }
 
     const int rot_units = (n_heads + (writes ? n_kv : 0)) * cph;
     const int v_units = writes ? n_kv * (hd / N) : 0;
@@ -165,14 +167,124 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
     }
 }
 
+// Four values rounded to bfloat16, as floats again / as the eight bytes to store.
+__device__ __forceinline__ float4 round_bf16(float4 v) {
+    return make_float4(__bfloat162float(__float2bfloat16_rn(v.x)),
+                       __bfloat162float(__float2bfloat16_rn(v.y)),
+                       __bfloat162float(__float2bfloat16_rn(v.z)),
+                       __bfloat162float(__float2bfloat16_rn(v.w)));
+}
+__device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
+    uint2 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(v.x, v.y);
+    h[1] = __floats2bfloat162_rn(v.z, v.w);
+    return raw;
+}
+
+// The rows are still in the parts a matrix product was cut into along K (float32
+// [n_parts][tokens][row width]): a thread adds up four values of each half of a head
+// in the order of the parts, rounds them to bfloat16 as the finished product would
+// have been, and goes on as above.  Rotated queries go to qkv; the keys and values
+// only to the pages.  gridDim.y blocks share a token, so that with few tokens more
+// than a handful of SMs pull the parts in.
+constexpr int PARTS_THREADS = 64;
+__global__ void __launch_bounds__(PARTS_THREADS)
+rope_store_parts_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                        const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_pool,
+                        __nv_bfloat16* __restrict__ v_pool, int n_heads, int n_kv, int hd,
+                        int block_size, int max_pos, long long pool_slots, int writes,
+                        const float* __restrict__ parts, int n_parts, size_t part_stride,
+                        int* status) {
+    chain_release();
+    const int t = blockIdx.x;
+    const int half = hd >> 1, qph = half / 4;            // groups of four per half head
+    int pos = positions[t];
+    const bool bad_pos = pos < 0 || pos >= max_pos;
+    if (bad_pos) pos = pos < 0 ? 0 : max_pos - 1;
+    const float* cr = cos_t + (size_t)pos * half;
+    const float* sr = sin_t + (size_t)pos * half;
+    const size_t width = (size_t)(n_heads + 2 * n_kv) * hd;
+    long long slot = writes ? (long long)slot_map[t] : 0;
+    const bool slot_ok = slot >= 0 && slot < pool_slots;
+    const long long page = slot / block_size, off = slot % block_size;
+    const long long n_pages = pool_slots / block_size;
+    const int rot_units = (n_heads + (writes ? n_kv : 0)) * qph;
+    const int v_units = writes ? n_kv * (hd / 4) : 0;
+    const int per_block = (rot_units + v_units + gridDim.y - 1) / gridDim.y;
+    const int u_end = min(rot_units + v_units, (int)(blockIdx.y + 1) * per_block);
+    chain_wait();
+    if (threadIdx.x == 0 && blockIdx.y == 0 && status) {
+        if (bad_pos) atomicOr(status, MLS_STATUS_BAD_POSITION);
+        if (writes && !slot_ok) atomicOr(status, MLS_STATUS_BAD_SLOT);
+    }
+    for (int u = blockIdx.y * per_block + threadIdx.x; u < u_end; u += blockDim.x) {
+        if (u < rot_units) {
+            const int head = u / qph, c = u - head * qph;
+            const size_t col = (size_t)head * hd + c * 4;
+            const size_t at[2] = {(size_t)t * width + col, (size_t)t * width + col + half};
+            float4 x[2];
+            sum_parts4_of<2, 8>(parts, at, n_parts, part_stride, x);
+            const float4 x1 = round_bf16(x[0]), x2 = round_bf16(x[1]);
+            const float4 cs = *reinterpret_cast<const float4*>(cr + c * 4);
+            const float4 sn = *reinterpret_cast<const float4*>(sr + c * 4);
+            float4 o1, o2;
+            o1.x = __fsub_rn(__fmul_rn(x1.x, cs.x), __fmul_rn(x2.x, sn.x));
+            o1.y = __fsub_rn(__fmul_rn(x1.y, cs.y), __fmul_rn(x2.y, sn.y));
+            o1.z = __fsub_rn(__fmul_rn(x1.z, cs.z), __fmul_rn(x2.z, sn.z));
+            o1.w = __fsub_rn(__fmul_rn(x1.w, cs.w), __fmul_rn(x2.w, sn.w));
+            o2.x = __fadd_rn(__fmul_rn(x2.x, cs.x), __fmul_rn(x1.x, sn.x));
+            o2.y = __fadd_rn(__fmul_rn(x2.y, cs.y), __fmul_rn(x1.y, sn.y));
+            o2.z = __fadd_rn(__fmul_rn(x2.z, cs.z), __fmul_rn(x1.z, sn.z));
+            o2.w = __fadd_rn(__fmul_rn(x2.w, cs.w), __fmul_rn(x1.w, sn.w));
+            __nv_bfloat16* dst = nullptr;
+            if (head < n_heads) {
+                dst = qkv + (size_t)t * width + col;
+            } else if (slot_ok) {
+                const int kvh = head - n_heads;
+                dst = k_pool + (((size_t)kvh * n_pages + page) * block_size + off) * hd + c * 4;
+            }
+            if (dst) {
+                *reinterpret_cast<uint2*>(dst) = pack_bf16x4(o1);
+                *reinterpret_cast<uint2*>(dst + half) = pack_bf16x4(o2);
+            }
+        } else if (slot_ok) {
+            const int w = u - rot_units;
+            const int per = hd / 4;
+            const int kvh = w / per, c = w - kvh * per;
+            const size_t at[1] = {(size_t)t * width + (size_t)(n_heads + n_kv + kvh) * hd + c * 4};
+            float4 x[1];
+            sum_parts4_of<1, 8>(parts, at, n_parts, part_stride, x);
+            *reinterpret_cast<uint2*>(
+                v_pool + (((size_t)kvh * n_pages + page) * block_size + off) * hd + c * 4) =
+                pack_bf16x4(x[0]);
+        }
+    }
+}
+
 MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const float* cos_t,
                            const float* sin_t, const int* slot_map, void* k_pool, void* v_pool,
                            int n_tokens, int n_heads, int n_kv, int hd, int block_size,
-                           int max_pos, long long pool_slots, int writes, int* status,
+                           int max_pos, long long pool_slots, int writes, const float* parts,
+                           int n_parts, long long part_stride, int* status,
                            cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return MLS_ERR_UNSUPPORTED;
     const int vec_n = dtype == MLS_BF16 ? 8 : 4;
+    if (parts) {
+        // rows still in parts: bfloat16 activations, whole float4s in every part
+        if (dtype != MLS_BF16 || (hd / 2) % 4 != 0 || n_parts < 1 || part_stride % 4 != 0)
+            return MLS_ERR_UNSUPPORTED;
+        const int units = ((n_heads + n_kv) * (hd / 2) + n_kv * hd) / 4;
+        int per_token = (units + PARTS_THREADS - 1) / PARTS_THREADS;
+        if (n_tokens * per_token > 592) per_token = (592 + n_tokens - 1) / n_tokens;
+        MLS_LAUNCH((rope_store_parts_kernel), dim3(n_tokens, per_token), dim3(PARTS_THREADS), 0,
+                   stream, (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map,
+                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_heads, n_kv, hd, block_size,
+                   max_pos, pool_slots, writes, parts, n_parts, (size_t)part_stride, status);
+        return launch_status();
+    }
     if ((hd / 2) % vec_n == 0) {
         const int units = ((n_heads + n_kv) * (hd / 2) + n_kv * hd) / vec_n;
         int vthreads = 32;

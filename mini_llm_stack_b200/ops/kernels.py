@@ -84,7 +84,7 @@ class SplitParts:
 
     def release(self) -> None:
         if self._ops is not None:
-            self._ops._delta_parts_busy = False
+            self._ops._parts_busy = False
             self._ops = None
 
     def float(self):
@@ -121,7 +121,7 @@ class Ops:
         self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _P, _P, _I, _I, _I, _P])
         self._rope_store = _decl(core, "mls_rope_store",
                                  [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
-                                  _LL, _I, _P, _P])
+                                  _LL, _I, _P, _I, _LL, _P, _P])
         self._attention_simt = _decl(core, "mls_attention_simt",
                                      [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _I, _LL, _P])
@@ -133,7 +133,7 @@ class Ops:
         self._attention_shapes: set = set()      # (kv heads, group size) of the mixers
         self._scratch: dict = {}
         self._gemm = None
-        self._delta_parts_busy = False
+        self._parts_busy = False
         self.attention_impl = os.environ.get("MLS_B200_ATTENTION", "auto")
         self.gemm_impl = os.environ.get("MLS_B200_GEMM", "auto")
         self.generation = 0          # grows whenever a buffer kernels were given moves
@@ -304,7 +304,7 @@ class Ops:
         if swap:
             splits = self._gemm_splits(m, n, k)
             if splits > 1:
-                tag = "gemm_delta_parts" if leave_parts else "gemm_partials"
+                tag = "gemm_kept_parts" if leave_parts else "gemm_partials"
                 partial = self.scratch(tag, splits * m * n)
         _need(not leave_parts or splits > 1, "gemm_bf16: no parts to leave")
         self.launches += 2 if splits > 1 and not leave_parts else 1
@@ -313,18 +313,19 @@ class Ops:
                           m, n, k, swap, splits, epilogue, _ptr(partial), _ptr(self.status),
                           self._stream()), "gemm_bf16")
         if leave_parts:
-            self._delta_parts_busy = True
+            self._parts_busy = True
             return SplitParts(partial[:splits * m * n].view(splits, m, n), self)
         return None
 
-    def linear_delta(self, a, w, out):
-        """A product whose result is only ever added to the residual stream: returns
-        ``out``, filled, or the product's K-parts (``SplitParts``) for the next
-        ``add_rmsnorm`` to add up, with ``out`` untouched."""
+    def linear_parts(self, a, w, out):
+        """A product for a consumer that can add up K-parts while it reads its input
+        anyway (``add_rmsnorm`` for what goes to the residual stream, ``rope_store``
+        for q, k and v): returns ``out``, filled, or the product's parts
+        (``SplitParts``) with ``out`` untouched."""
         m, k = a.shape
         n = w.shape[0]
         if (0 < m <= 64 and n % 4 == 0 and w.dtype == torch.bfloat16
-                and not self._delta_parts_busy
+                and not self._parts_busy
                 and w.shape == (n, k) and a.is_contiguous() and w.is_contiguous()
                 and self._use_own_gemm(m, n, k) and self._gemm_splits(m, n, k) > 1):
             a16 = a if a.dtype == torch.bfloat16 else a.to(torch.bfloat16)
@@ -357,8 +358,16 @@ class Ops:
             return
         self._gemm_bf16(a, w_interleaved, out, m, n, k, epilogue=1)
 
+    def rope_takes_parts(self, hd: int) -> bool:
+        """Whether ``rope_store`` can read its rows from a product's K-parts."""
+        return self.act_dtype == torch.bfloat16 and (hd // 2) % 8 == 0
+
     def rope_store(self, qkv, positions, cos, sin, slot_map, k_pool, v_pool, n_tokens: int,
-                   n_heads: int, n_kv: int, hd: int, max_pos: int, writes: bool) -> None:
+                   n_heads: int, n_kv: int, hd: int, max_pos: int, writes: bool,
+                   parts=None) -> None:
+        """Rotate q and k, store rotated k and raw v in the pages, leave rotated q in
+        ``qkv``.  With ``parts`` (``SplitParts`` of the projection) the rows are
+        read from there instead of from ``qkv``."""
         _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv) * hd,
               "rope_store: bad qkv")
         _need(k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype,
@@ -368,12 +377,21 @@ class Ops:
         _need(kvh == n_kv and hd2 == hd, "rope_store: pool shape does not fit the heads")
         _need(cos.shape == (max_pos, hd // 2) and cos.dtype == torch.float32,
               "rope_store: bad tables")
+        pp, n_parts, stride = None, 0, 0
+        if parts is not None:
+            _need(self.rope_takes_parts(hd) and qkv.dtype == torch.bfloat16
+                  and tuple(parts.shape) == tuple(qkv.shape) and parts.parts.is_contiguous(),
+                  "rope_store: these parts cannot be read")
+            pp, n_parts = parts.parts.data_ptr(), parts.parts.shape[0]
+            stride = qkv.shape[0] * qkv.shape[1]
         self.launches += 1
         _check(self._rope_store(_ptr(qkv), _code(qkv.dtype), _ptr(positions), _ptr(cos),
                                 _ptr(sin), _ptr(slot_map), _ptr(k_pool), _ptr(v_pool),
                                 n_tokens, n_heads, n_kv, hd, block, max_pos,
-                                pages * block, 1 if writes else 0, _ptr(self.status),
-                                self._stream()), "rope_store")
+                                pages * block, 1 if writes else 0, pp, n_parts, stride,
+                                _ptr(self.status), self._stream()), "rope_store")
+        if parts is not None:
+            parts.release()
 
     def require_attention(self, hd: int, n_heads: int = 0, n_kv: int = 0) -> None:
         """Make sure attention kernels for this head size exist, or say why not."""

@@ -56,11 +56,18 @@ class GroupedQueryAttention(Mixer):
         hd = self.head_dim
         width = (self.n_heads + 2 * self.n_kv_heads) * hd
         qkv = rt.buffer("qkv", (t, width), rt.act_dtype)
-        rt.ops.linear(h, self.wqkv, qkv)
-        self.position.rotate_and_store(qkv, step, cache, self.n_heads,
-                                       self.n_kv_heads)
+        if getattr(self.position, "takes_parts", False):
+            # the projection may stay in the parts it was cut into along K: the
+            # rotation adds them up as it reads them
+            src = rt.ops.linear_parts(h, self.wqkv, qkv)
+            self.position.rotate_and_store(qkv, step, cache, self.n_heads, self.n_kv_heads,
+                                           parts=None if src is qkv else src)
+        else:
+            rt.ops.linear(h, self.wqkv, qkv)
+            self.position.rotate_and_store(qkv, step, cache, self.n_heads,
+                                           self.n_kv_heads)
         o = rt.buffer("attn_out", (t, self.n_heads * hd), rt.act_dtype)
         rt.ops.paged_attention(qkv, o, cache, step, self.n_heads, self.n_kv_heads,
                                hd, self.scale, self.window or 0)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
-        return rt.ops.linear_delta(o, self.wo, delta)
+        return rt.ops.linear_parts(o, self.wo, delta)

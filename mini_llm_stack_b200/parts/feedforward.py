@@ -54,4 +54,4 @@ class SwiGLUFeedForward(FeedForward):
             rt.ops.linear(h, self.w_gate_up, gu)
             rt.ops.swiglu(gu, act)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
-        return rt.ops.linear_delta(act, self.w_down, delta)
+        return rt.ops.linear_parts(act, self.w_down, delta)

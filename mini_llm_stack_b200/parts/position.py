@@ -40,8 +40,14 @@ class RotaryPosition(PositionEncoding):
         self.cos = cos.contiguous().to(runtime.device)
         self.sin = sin.contiguous().to(runtime.device)
 
+    @property
+    def takes_parts(self) -> bool:
+        """Whether ``rotate_and_store`` accepts ``parts`` (the projection left as the
+        parts of a cut along K) in place of filled ``qkv`` rows."""
+        return self.runtime.ops.rope_takes_parts(self.head_dim)
+
     def rotate_and_store(self, qkv, step: StepContext, cache: CacheHandle,
-                         n_heads: int, n_kv_heads: int) -> None:
+                         n_heads: int, n_kv_heads: int, parts=None) -> None:
         """Rotate q and k of ``qkv`` in place; store rotated k and raw v.
 
         The keys and values of this step's tokens go into the pages before
@@ -53,4 +59,4 @@ class RotaryPosition(PositionEncoding):
         self.runtime.ops.rope_store(
             qkv, step.positions, self.cos, self.sin, g.slot_map,
             cache.k_pool, cache.v_pool, step.n_tokens, n_heads, n_kv_heads,
-            self.head_dim, self.max_positions, cache.writes)
+            self.head_dim, self.max_positions, cache.writes, parts=parts)

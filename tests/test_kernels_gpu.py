@@ -145,9 +145,9 @@ def test_product_left_as_parts_is_summed_by_the_next_norm(rts, m, n, k):
     out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
     ops.gemm_impl = "tcgen05"
     try:
-        parts = ops.linear_delta(a, wp, out)
+        parts = ops.linear_parts(a, wp, out)
         assert isinstance(parts, SplitParts) and parts.shape == (m, n)
-        again = ops.linear_delta(a, wp, out)              # the buffer is taken: the ordinary way
+        again = ops.linear_parts(a, wp, out)              # the buffer is taken: the ordinary way
         assert again is out
     finally:
         ops.gemm_impl = "auto"
@@ -168,7 +168,7 @@ def test_product_left_as_parts_is_summed_by_the_next_norm(rts, m, n, k):
     want_h = P.plain_rmsnorm((x + want).cpu(), g.cpu(), 1e-5)
     assert torch.allclose(h.float().cpu(), want_h, rtol=8e-3, atol=8e-3)
     assert torch.equal(hg[0], h[m - 1]) and torch.equal(hg[1], h[0])
-    assert not ops._delta_parts_busy                      # given back by the norm
+    assert not ops._parts_busy                      # given back by the norm
     assert torch.allclose(out.float(), want, rtol=1e-2, atol=5e-3 * scale)   # the ordinary way's result
 
 
@@ -265,6 +265,35 @@ def test_rope_store(rts, dtype, heads, kv, hd, theta, block):
     ops.rope_store(got2, pos.to(DEV), cos.to(DEV), sin.to(DEV), slots.to(DEV), k_pool, v_pool, t,
                    heads, kv, hd, max_pos, False)
     assert torch.equal(k2, k_pool) and torch.equal(got2[:, :heads * hd], got[:, :heads * hd])
+
+
+@pytest.mark.parametrize("heads, kv, hd, block, n_parts", [(8, 2, 128, 16, 6), (3, 1, 32, 8, 3),
+                                                           (5, 5, 48, 16, 2), (4, 2, 64, 4, 1)])
+def test_rope_store_reads_rows_from_the_parts_of_a_product(rts, heads, kv, hd, block, n_parts):
+    """Rows left as float32 K-parts give, bit for bit, what the summed and rounded
+    rows give; the keys and values in qkv itself are not needed."""
+    from mini_llm_stack_b200.ops.kernels import SplitParts
+    ops = rts[torch.bfloat16].ops
+    assert ops.rope_takes_parts(hd)
+    max_pos, pages, t = 200, 40, 9
+    width = (heads + 2 * kv) * hd
+    cos, sin = (x.to(DEV) for x in P.plain_rotary_tables(hd, max_pos, 5e5))
+    parts = rand((n_parts, t, width), torch.float32, 31)
+    summed = parts[0].clone()
+    for k in range(1, n_parts):
+        summed += parts[k]
+    qkv = summed.to(torch.bfloat16)
+    pos = torch.randint(0, max_pos, (t,), generator=torch.Generator().manual_seed(32)).int().to(DEV)
+    slots = torch.randperm(pages * block, generator=torch.Generator().manual_seed(33))[:t].int().to(DEV)
+    pools = [torch.full((kv, pages, block, hd), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    ops.rope_store(qkv, pos, cos, sin, slots, pools[0], pools[1], t, heads, kv, hd, max_pos, True)
+    got = torch.full((t, width), 3.0, dtype=torch.bfloat16, device=DEV)
+    ops.rope_store(got, pos, cos, sin, slots, pools[2], pools[3], t, heads, kv, hd, max_pos, True,
+                   parts=SplitParts(parts, None))
+    ops.check_status()
+    assert torch.equal(got[:, :heads * hd], qkv[:, :heads * hd])
+    assert torch.equal(pools[0], pools[2]) and torch.equal(pools[1], pools[3])
+    assert bool((got[:, heads * hd:] == 3.0).all())
 
 
 # ----------------------------------------------------------------------- attention
