@@ -103,7 +103,7 @@ template <> struct Vec16<__nv_bfloat16> {
 // The same work as rope_store_kernel for head sizes whose halves are whole 16-byte
 // chunks; one thread rotates one chunk pair of one head, or copies one chunk of v.
 template <typename T>
-__global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void __launch_bounds__(512, 3) rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                       const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t,
                                       const int* __restrict__ slot_map, T* __restrict__ k_pool,
@@ -137,14 +137,20 @@ __global__ void rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict
         if (u < rot_units) {
             const int head = u / cph, c = u - head * cph;
             T* hp = row + (size_t)head * hd + c * N;
-            float x1[N], x2[N], o1[N], o2[N];
+            float x1[N], x2[N], o1[N], o2[N], cs[N], sn[N];
             Vec16<T>::load(hp, x1);
             Vec16<T>::load(hp + half, x2);
 #pragma unroll
+            for (int e = 0; e < N; e += 4) {          // half is a multiple of N: whole float4s
+                const float4 c4 = *reinterpret_cast<const float4*>(cr + c * N + e);
+                const float4 s4 = *reinterpret_cast<const float4*>(sr + c * N + e);
+                cs[e] = c4.x, cs[e + 1] = c4.y, cs[e + 2] = c4.z, cs[e + 3] = c4.w;
+                sn[e] = s4.x, sn[e + 1] = s4.y, sn[e + 2] = s4.z, sn[e + 3] = s4.w;
+            }
+#pragma unroll
             for (int e = 0; e < N; ++e) {
-                const float cs = cr[c * N + e], sn = sr[c * N + e];
-                o1[e] = __fsub_rn(__fmul_rn(x1[e], cs), __fmul_rn(x2[e], sn));
-                o2[e] = __fadd_rn(__fmul_rn(x2[e], cs), __fmul_rn(x1[e], sn));
+                o1[e] = __fsub_rn(__fmul_rn(x1[e], cs[e]), __fmul_rn(x2[e], sn[e]));
+                o2[e] = __fadd_rn(__fmul_rn(x2[e], cs[e]), __fmul_rn(x1[e], sn[e]));
             }
             if (head < n_heads) {
                 Vec16<T>::store(hp, o1);

@@ -117,7 +117,7 @@ class Ops:
         core = self._load("core")
         self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _P, _P])
         self._add_rmsnorm = _decl(core, "mls_add_rmsnorm",
-                                  [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _I, _LL, _P])
+                                  [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _I, _LL, _P, _P])
         self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _P, _P, _I, _I, _I, _P])
         self._rope_store = _decl(core, "mls_rope_store",
                                  [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
@@ -216,7 +216,7 @@ class Ops:
         self.launches += 1
         _check(self._add_rmsnorm(_ptr(x), dp, dcode, _ptr(weight), _code(weight.dtype),
                                  float(eps), _ptr(h), _code(h.dtype), t, d, None, parts, stride,
-                                 self._stream()), "add_rmsnorm")
+                                 _ptr(self.status), self._stream()), "add_rmsnorm")
         if isinstance(delta, SplitParts):
             delta.release()
 
@@ -229,7 +229,8 @@ class Ops:
         self.launches += 1
         _check(self._add_rmsnorm(_ptr(x), dp, dcode, _ptr(weight), _code(weight.dtype),
                                  float(eps), _ptr(h), _code(h.dtype), n_rows, d, _ptr(rows),
-                                 parts, stride, self._stream()), "gather_add_rmsnorm")
+                                 parts, stride, _ptr(self.status), self._stream()),
+               "gather_add_rmsnorm")
         if isinstance(delta, SplitParts):
             delta.release()
 

@@ -73,6 +73,34 @@ def test_add_rmsnorm(rts, dtype, rows, d, eps):
     assert torch.allclose(hg.float().cpu(), want_h[[rows - 1, 0]], rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows, d", [(2048, 4096), (301, 1000), (777, 512), (296, 2056)])
+def test_add_rmsnorm_of_many_rows_gives_the_bits_of_few_rows(rts, dtype, rows, d):
+    """Prompts take a kernel that streams rows through shared memory; a row's result
+    is bit for bit what it is in a batch of a few rows."""
+    ops = rts[dtype].ops
+    x = rand((rows, d), torch.float32, 41, 2.0)
+    delta = rand((rows, d), dtype, 42)
+    w = 1 + rand((d,), dtype, 43, 0.1)
+    h = torch.empty((rows, d), dtype=dtype, device=DEV)
+    xx = x.clone()
+    ops.add_rmsnorm(xx, delta, w, 1e-5, h)
+    ops.check_status()
+    assert torch.equal(xx, x + delta.float())
+    pick = torch.tensor([0, 1, rows // 2, rows - 5, rows - 1], device=DEV)
+    x_few = x[pick].clone()
+    h_few = torch.empty((5, d), dtype=dtype, device=DEV)
+    ops.add_rmsnorm(x_few, delta[pick].contiguous(), w, 1e-5, h_few)
+    assert torch.equal(h[pick], h_few)
+    want = P.plain_rmsnorm((x + delta.float()).cpu(), w.cpu(), 1e-5)
+    tol = 2e-6 if dtype == torch.float32 else 8e-3
+    assert torch.allclose(h.float().cpu(), want, rtol=tol, atol=tol)
+    # without a pending delta
+    h2 = torch.empty((rows, d), dtype=dtype, device=DEV)
+    ops.add_rmsnorm(xx, None, w, 1e-5, h2)
+    assert torch.equal(h2, h)
+
+
 def test_norm_weight_may_stay_float32_in_a_bfloat16_run(rts):
     ops = rts[torch.bfloat16].ops
     x = rand((4, 80), torch.float32, 6)
@@ -265,6 +293,36 @@ def test_rope_store(rts, dtype, heads, kv, hd, theta, block):
     ops.rope_store(got2, pos.to(DEV), cos.to(DEV), sin.to(DEV), slots.to(DEV), k_pool, v_pool, t,
                    heads, kv, hd, max_pos, False)
     assert torch.equal(k2, k_pool) and torch.equal(got2[:, :heads * hd], got[:, :heads * hd])
+
+
+@pytest.mark.parametrize("heads, kv, hd, block, t", [(32, 8, 128, 16, 2048), (3, 1, 32, 8, 301),
+                                                     (5, 5, 48, 16, 700), (4, 2, 64, 4, 296)])
+def test_rope_store_of_many_tokens_gives_the_bits_of_few_tokens(rts, heads, kv, hd, block, t):
+    """Prompts take a kernel that streams rows through shared memory (bfloat16, head
+    halves of whole chunks); other sizes take the ordinary one: the same bits."""
+    ops = rts[torch.bfloat16].ops
+    max_pos = t + 50
+    pages = (t + block - 1) // block + 3
+    width = (heads + 2 * kv) * hd
+    cos, sin = (x.to(DEV) for x in P.plain_rotary_tables(hd, max_pos, 5e5))
+    qkv = rand((t, width), torch.bfloat16, 51)
+    pos = torch.randint(0, max_pos, (t,), generator=torch.Generator().manual_seed(52)).int().to(DEV)
+    slots = torch.randperm(pages * block, generator=torch.Generator().manual_seed(53))[:t].int().to(DEV)
+    pools = [torch.full((kv, pages, block, hd), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
+    many = qkv.clone()
+    ops.rope_store(many, pos, cos, sin, slots, pools[0], pools[1], t, heads, kv, hd, max_pos, True)
+    ops.check_status()
+    few = qkv.clone()
+    for at in range(0, t, 100):
+        n = min(100, t - at)
+        ops.rope_store(few[at:at + n], pos[at:at + n], cos, sin, slots[at:at + n], pools[2], pools[3],
+                       n, heads, kv, hd, max_pos, True)
+    assert torch.equal(many[:, :heads * hd], few[:, :heads * hd])
+    assert torch.equal(pools[0], pools[2]) and torch.equal(pools[1], pools[3])
+    reader = qkv.clone()                                  # a call that only rotates its queries
+    k_before = pools[0].clone()
+    ops.rope_store(reader, pos, cos, sin, slots, pools[0], pools[1], t, heads, kv, hd, max_pos, False)
+    assert torch.equal(reader[:, :heads * hd], many[:, :heads * hd]) and torch.equal(k_before, pools[0])
 
 
 @pytest.mark.parametrize("heads, kv, hd, block, n_parts", [(8, 2, 128, 16, 6), (3, 1, 32, 8, 3),
