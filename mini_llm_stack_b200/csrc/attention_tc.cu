@@ -106,8 +106,9 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     volatile uint32_t* tmem_slot =
         reinterpret_cast<volatile uint32_t*>(gbase + (bars - base) + 8 * N_BARS);
 
-    // which request and which 128-row tile of it; the last rows see the most keys
-    int r = 0, tile = blockIdx.x, q_len = 0, rows = 0;
+    // which request and which 128-row tile of it; the last rows see the most keys and
+    // go first, for all kv heads (blockIdx.x) before the next tile
+    int r = 0, tile = blockIdx.y, q_len = 0, rows = 0;
     for (; r < P.n_req; ++r) {
         q_len = P.cu_q[r + 1] - P.cu_q[r];
         rows = q_len * P.group;
@@ -117,7 +118,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     }
     if (r >= P.n_req) return;
     tile = (rows + ROWS - 1) / ROWS - 1 - tile;
-    const int kvh = blockIdx.y;
+    const int kvh = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
     const int row0 = tile * ROWS;
@@ -508,7 +509,7 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.scale_log2 = scale * LOG2E;
     P.status = status;
     P.n_pages = pool_pages;
-    MLS_LAUNCH((attention_tc_kernel), dim3(n_tiles, n_kv), dim3(THREADS), SMEM_BYTES, stream, P,
+    MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, n_tiles), dim3(THREADS), SMEM_BYTES, stream, P,
                kmap, vmap, kmap_wide, vmap_wide);
     return launch_status();
 #else
