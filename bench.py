@@ -220,6 +220,59 @@ def serve_workload(name: str) -> int:
     return 0
 
 
+def write_timeline(args, torch, runner, cache, ops, ctx, rand_tokens, Entry) -> int:
+    """Start and end of every kernel of a decode step and of a prefill step.
+
+    Kernels overlap where one was launched under its predecessor, which a list of
+    durations cannot show.  Times are relative to the step's first kernel; numbers
+    taken under the profiler are for reading the schedule, not for reporting."""
+    from torch.autograd import DeviceType
+    from torch.profiler import ProfilerActivity, profile
+
+    ids = [f"t{i}" for i in range(args.batch)]
+    for r in ids:
+        cache.admit(r)
+        assert cache.reserve(r, ctx - 16)
+        cache.commit(r, ctx - 16)
+    out = torch.empty(args.batch, dtype=torch.int32, device="cuda:0")
+
+    def decode():
+        e = [Entry(r, [5], [0]) for r in ids]
+        runner.reserve(e)
+        ops.sample(runner.step(e), None, None, out)
+
+    def prefill():
+        e = [Entry("prefill", rand_tokens(PREFILL_TOKENS), [PREFILL_TOKENS - 1])]
+        runner.reserve(e)
+        runner.step(e)
+        runner.release("prefill")
+
+    lines = []
+    for name, fn, warm in (("decode step", decode, 6), ("prefill step", prefill, 3)):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        evs = sorted((ev.time_range.start, ev.time_range.end, ev.name)
+                     for ev in prof.events() if ev.device_type == DeviceType.CUDA)
+        if fn is decode:
+            for r in ids:
+                runner.release(r)
+        t0 = evs[0][0]
+        lines.append(f"# {name}: batch {args.batch}, context {ctx}, {args.layers} layers, "
+                     f"{len(evs)} kernels, {evs[-1][1] - t0:.1f} us")
+        lines.append("start_us end_us dur_us kernel")
+        for a, b, n in evs:
+            short = n.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0]
+            lines.append(f"{a - t0:8.1f} {b - t0:8.1f} {b - a:7.1f} {short[:60]}")
+    with open(args.timeline, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    print(json.dumps({"timeline": args.timeline, "lines": len(lines)}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -230,6 +283,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=MODEL["max_seq_len"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--timeline", default=None, metavar="FILE",
+                    help="instead of timing, record when each kernel of one decode step and of "
+                         "one prefill step starts and ends (torch.profiler) and write the table "
+                         "to FILE; use few --layers")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed_1b", "poisson_7b"],
                     help="decode: the contract's line; the others serve a request mix through "
                          "the scheduler and print their own line")
@@ -277,6 +334,9 @@ def main() -> int:
 
     def rand_tokens(n):
         return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+
+    if args.timeline:
+        return write_timeline(args, torch, runner, cache, ops, ctx, rand_tokens, Entry)
 
     clocks = ClockSampler()
     clocks.start()
