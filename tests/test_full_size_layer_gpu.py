@@ -60,3 +60,29 @@ def test_own_gemm_everywhere_gives_the_same_logits(big, monkeypatch):
     assert rp.model.runtime.ops.library_launches == 0    # no product went to the library
     assert_close(rp.logits("a"), plain_logits(w, cfg, toks["a"], "bfloat16"), "bfloat16",
                  "tcgen05 GEMM for every product")
+
+
+def test_chained_launches_do_not_change_a_bit(big):
+    """Kernels that start under their predecessors (and fetch weights and old keys
+    before they wait) must give what plainly ordered launches give, every time: a
+    kernel that read its input too early would show as a difference or as a run
+    that differs from the next."""
+    folder, cfg, w = big
+    toks = {r: tokens_for(1000, 600, 5 + i) for i, r in enumerate("abc")}
+
+    def run(chained):
+        rp = Replayer(folder, "bfloat16", num_blocks=130)
+        ops = rp.model.runtime.ops
+        ops.CHAINED_UP_TO = 256 if chained else -1
+        rp.step([("a", 500), ("b", 300)], toks)           # plain launches either way (many tokens)
+        rp.step([("a", 40), ("b", 7), ("c", 100)], toks)  # a small mixed step
+        for _ in range(30):
+            rp.step([("a", 1), ("b", 1), ("c", 1)], toks)  # decoded tokens, graphs after the second
+        assert ops._chained == chained
+        return {r: rp.logits(r) for r in "abc"}
+
+    plain = run(False)
+    for _ in range(3):
+        chained = run(True)
+        for r in "abc":
+            assert torch.equal(chained[r], plain[r]), f"request {r} differs under chained launches"
