@@ -142,7 +142,10 @@ def test_linear_with_float32_weights_in_a_bfloat16_run(rts):
 
 @pytest.mark.parametrize("m, n, k", [(1, 128, 64), (8, 6144, 4096), (37, 257, 200), (300, 96, 1000),
                                      (64, 1000, 4096), (2048, 512, 1024), (17, 4096, 14336),
-                                     (129, 300, 72), (65, 128, 8), (33, 97, 4096)])
+                                     (129, 300, 72), (65, 128, 8), (33, 97, 4096),
+                                     # row counts whose 128-row tiles do not fill whole rounds of
+                                     # CTAs: tiles of 96 + 128 rows, and of 64 + 96
+                                     (2, 128256, 128), (5, 22016, 256), (64, 28672, 64)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("impl", ["tcgen05", "cublas"])
 def test_linear_bf16(rts, m, n, k, out_dtype, impl):
@@ -201,6 +204,7 @@ def test_product_left_as_parts_is_summed_by_the_next_norm(rts, m, n, k):
 
 
 @pytest.mark.parametrize("m, inter, k", [(1, 14336, 4096), (8, 176, 64), (64, 256, 96), (33, 4096, 4096),
+                                         (8, 11008, 128), (3, 10000, 64),
                                           (300, 272, 200), (2048, 1024, 512), (129, 14336, 1024)])
 def test_gate_up_projection_with_swiglu_epilogue(rts, m, inter, k):
     ops = rts[torch.bfloat16].ops
