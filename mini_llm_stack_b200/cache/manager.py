@@ -18,6 +18,7 @@ Slots with a ``FixedState`` spec share the request's state slot.
 
     reserve(req, n)  -> bool   pages for the next n tokens, all groups or none
     commit(req, n)             the n tokens are stored; windows release pages
+    truncate(req, n)           only the first n tokens stay; whole pages past them go back
     free(req)                  everything back
 """
 
@@ -244,6 +245,38 @@ class CacheManager:
                 g.pool.give(list(reversed(pages)), owner)
                 g.table[rec.row, first:dead] = -1
                 rec.released[g.gid] = dead
+
+    def truncate(self, owner, n_tokens: int) -> None:
+        """Forget the tokens past the first ``n_tokens``; whole pages past them go back.
+
+        (The reference never shortens a sequence; a caller that takes back tokens it
+        had stored, e.g. after rejecting a guessed continuation, needs it.)  A window
+        group that has released pages the shorter sequence would read again, and a
+        fixed-size state, cannot go back: both are refused.
+        """
+        rec = self._records[owner]
+        if not 0 <= n_tokens <= rec.length:
+            raise CacheError(f"request {owner!r} holds {rec.length} tokens, not {n_tokens}")
+        if n_tokens == rec.length:
+            return
+        if self.fixed:
+            raise CacheError("a state of fixed size cannot be taken back to an earlier token")
+        for g in self.paged:
+            w = g.spec.window
+            if w is not None and rec.released[g.gid] * self.block_size > max(0, n_tokens - w + 1):
+                raise CacheError(
+                    f"request {owner!r}: pages behind the window of {w} were given back; "
+                    f"it cannot be cut to {n_tokens} tokens")
+        keep = self.pages_for(n_tokens)
+        for g in self.paged:
+            n = rec.n_pages[g.gid]
+            first = max(keep, rec.released[g.gid])
+            if n > first:
+                pages = [int(p) for p in g.table[rec.row, first:n]]
+                g.pool.give(list(reversed(pages)), owner)
+                g.table[rec.row, first:n] = -1
+                rec.n_pages[g.gid] = first
+        rec.length = n_tokens
 
     def free(self, owner) -> None:
         """Give back everything ``owner`` holds (serve/kv_cache.py:75-77)."""

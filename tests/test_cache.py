@@ -117,6 +117,43 @@ def test_window_gives_pages_back_when_passed():
     c.check()
 
 
+def test_truncate_gives_whole_pages_back():
+    c = _mgr(specs=(FULL, FULL), num_blocks=8, block_size=4)
+    c.admit("r")
+    assert c.reserve("r", 14)
+    c.commit("r", 14)
+    assert c.num_free_pages() == 4
+    c.truncate("r", 14)                                   # nothing to do
+    c.truncate("r", 9)                                    # pages 0..2 stay, page 3 goes back
+    assert c.length("r") == 9 and c.pages_of("r", 0)[:3] == [0, 1, 2] and c.num_free_pages() == 5
+    c.check()
+    assert c.reserve("r", 4)                              # grows again from token 9, page 3 again
+    c.commit("r", 4)
+    assert c.pages_of("r", 0) == [0, 1, 2, 3]
+    c.truncate("r", 0)
+    assert c.length("r") == 0 and c.num_free_pages() == 8
+    with pytest.raises(CacheError):
+        c.truncate("r", 1)
+    c.check()
+    c.free("r")
+    # a window that has let pages go cannot be cut back to where it would read them
+    w = _mgr(specs=(FULL, WIN), num_blocks=16, block_size=4, max_seq_len=64)
+    w.admit("r")
+    assert w.reserve("r", 30)
+    w.commit("r", 30)                                     # keys < 21 are gone: five pages
+    w.truncate("r", 29)                                   # reads keys >= 20: all still there
+    with pytest.raises(CacheError, match="window"):
+        w.truncate("r", 20)
+    w.check()
+    # state of fixed size cannot go back either
+    f = _mgr(specs=(FULL, FixedState((3,))), num_blocks=8, block_size=4)
+    f.admit("r")
+    assert f.reserve("r", 5)
+    f.commit("r", 5)
+    with pytest.raises(CacheError, match="fixed size"):
+        f.truncate("r", 3)
+
+
 def test_step_arrays():
     c = _mgr(num_blocks=8, block_size=4, max_seq_len=32)
     c.admit("a")
@@ -200,6 +237,14 @@ def test_random_orders_lose_nothing(seed):
                     assert c.length(r) == live[r]
                 else:
                     assert before == [g.pool.num_free for g in c.paged]
+        elif act < 0.88 and live:
+            r = rng.choice(list(live))
+            n = rng.randint(0, live[r])
+            try:
+                c.truncate(r, n)
+                live[r] = n
+            except CacheError:
+                assert any(g.spec.window for g in c.paged)    # only a window may refuse
         elif live:
             r = rng.choice(list(live))
             c.free(r)
