@@ -371,9 +371,10 @@ def main() -> int:
                "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ------------------------------------------------------------------- decode
-    def decode_run(batch, n_warm, n_timed):
-        """Device time of one decode step with ``batch`` requests that end at ``ctx``."""
-        start = ctx - (n_warm + n_timed)
+    def decode_run(batch, n_warm, n_timed, end=None):
+        """Device time of one decode step with ``batch`` requests that end at ``end``
+        (the context length by default)."""
+        start = (end or ctx) - (n_warm + n_timed)
         ids = [f"d{batch}_{i}" for i in range(batch)]
         for r in ids:
             cache.admit(r)
@@ -405,6 +406,21 @@ def main() -> int:
         for b in (1, 64):
             pms, _, _ = decode_run(b, 3, max(8, steps // 4))
             points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        if ctx > 1024:                           # the same three batches early in a sequence
+            for b in (1, 8, 64):
+                pms, _, _ = decode_run(b, 3, max(8, steps // 4), end=1024)
+                points[f"decode_b{b}_ctx1024"] = round(b / pms * 1e3, 1)
+
+        def prefill_in_four():                   # the same prompt in four portions of 512
+            toks = rand_tokens(PREFILL_TOKENS)
+            for at in range(0, PREFILL_TOKENS, 512):
+                e = [Entry("prefill", toks[at:at + 512], [511])]
+                runner.reserve(e)
+                runner.step(e)
+            runner.release("prefill")
+
+        four_ms = sorted(timed(prefill_in_four, 1, 1)[0] for i in range(5))[2]
+        points["prefill_4x512"] = round(PREFILL_TOKENS / four_ms * 1e3, 1)
 
     # ---------------------------------------------------- end to end (Engine API)
     # every request must still be decoding when the last one has finished its

@@ -280,7 +280,7 @@ class Ops:
         # first weights while the kernel before it still runs; more rows go to the
         # library (as the reference's nn.Linear does) unless the kernel fuses work
         # (``linear_swiglu``)
-        return m <= 32
+        return m <= 64
 
     def _gemm_splits(self, m: int, n: int, k: int) -> int:
         """Parts along K for the weight-major orientation (M <= 64): the weights are
