@@ -10,12 +10,14 @@
 // keys 128 at a time (a tcgen05.mma costs about the same whatever its width, so
 // wide tiles pay):
 //   warp 0      brings keys and values in with TMA, one copy per page and 64-wide half,
-//               into a ring of three key tiles and a ring of two value tiles;
+//               into a ring of two key tiles and a ring of two value tiles;
 //   warp 1      issues S = Q K^T and O += P V (tcgen05.mma), accumulators in TMEM;
-//   warps 2..5  one thread per row: read S from TMEM, scale, mask, exponentiate, write P
-//               to shared memory as the next product's operand, rescale O when the
-//               running maximum has grown by more than 2^8, and store O at the end.
-// S is double-buffered in TMEM, so the next tile's Q K^T runs during the softmax.
+//   warps 2..9  two threads per row, each half of the tile's keys: read S from TMEM, mask,
+//               exponentiate, write P to shared memory as the next product's operand,
+//               rescale O when the running maximum has grown by more than 2^8, and
+//               store O at the end.
+// S is double-buffered in TMEM and P in shared memory, so the next tile's Q K^T and
+// this tile's P V run during the next tile's softmax.
 // Every wait is bounded and reports MLS_STATUS_TIMEOUT.
 #include "common.cuh"
 #include "tma.cuh"
@@ -41,10 +43,12 @@ constexpr int HALVES = HD / 64;
 constexpr int BLOCK = 128 * 128;                 // bytes of [128 rows][64 elements]: 16 KB
 constexpr int KBLOCK = BN * 128;                 // bytes of [128 keys][64 elements]: 16 KB
 constexpr int Q_BYTES = HALVES * BLOCK;          // per chain
-constexpr int P_BYTES = (BN / 64) * BLOCK;       // per chain: [128 rows][128 keys]
+constexpr int P_BYTES = (BN / 64) * BLOCK;       // per chain and buffer: [128 rows][128 keys]
+constexpr int P_BUFS = 2;                        // the softmax writes P(j+1) while P(j) V runs
 constexpr int K_STAGE = HALVES * KBLOCK, V_STAGE = HALVES * KBLOCK;
-constexpr int K_STAGES = 3, V_STAGES = 2;        // keys are needed a product earlier than values
-constexpr int THREADS = 64 + 128 * CHAINS;
+constexpr int K_STAGES = 2, V_STAGES = 2;
+constexpr int SOFTMAX_THREADS = 256 * CHAINS;      // two warps share 32 rows, half the keys each
+constexpr int THREADS = 64 + SOFTMAX_THREADS;
 constexpr int TMEM_COLS = 512;                   // per chain S0 | S1, then per chain O
 constexpr int COL_S = 0, COL_O = CHAINS * 2 * BN;
 static_assert(COL_O + CHAINS * HD <= TMEM_COLS, "tensor memory columns");
@@ -54,10 +58,12 @@ constexpr float RESCALE_STEP = 8.0f;             // log2: P stays below 2^8
 // barrier slots
 constexpr int B_K_FULL = 0, B_K_EMPTY = K_STAGES, B_V_FULL = 2 * K_STAGES,
               B_V_EMPTY = B_V_FULL + V_STAGES, B_S_FULL = B_V_EMPTY + V_STAGES,       // [chain][2]
-              B_S_EMPTY = B_S_FULL + 2 * CHAINS, B_P_FULL = B_S_EMPTY + 2 * CHAINS,   // [chain]
-              B_P_EMPTY = B_P_FULL + CHAINS, B_Q_FULL = B_P_EMPTY + CHAINS, N_BARS = B_Q_FULL + 1;
+              B_S_EMPTY = B_S_FULL + 2 * CHAINS, B_P_FULL = B_S_EMPTY + 2 * CHAINS,   // [chain][buf]
+              B_P_EMPTY = B_P_FULL + P_BUFS * CHAINS, B_Q_FULL = B_P_EMPTY + P_BUFS * CHAINS,
+              N_BARS = B_Q_FULL + 1;
 // no alignment slack: two CTAs must fit one SM; the kernel checks the alignment
-constexpr int SMEM_BYTES = CHAINS * (Q_BYTES + P_BYTES) + K_STAGES * K_STAGE + V_STAGES * V_STAGE +
+constexpr int SMEM_BYTES = CHAINS * (Q_BYTES + P_BUFS * P_BYTES) + K_STAGES * K_STAGE +
+                           V_STAGES * V_STAGE +
                            8 * N_BARS + 16;
 
 struct Params {
@@ -93,6 +99,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     chain_release();
     chain_wait();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ float row_max[2][2][128];         // [tile parity][half of the keys][row]
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {                          // the swizzled tiles need this alignment
         if (threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_SMEM);
@@ -100,7 +107,7 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     }
     uint8_t* gbase = smem_raw;
     const uint32_t q_smem = base, p_smem = base + CHAINS * Q_BYTES,
-                   k_smem = p_smem + CHAINS * P_BYTES, v_smem = k_smem + K_STAGES * K_STAGE;
+                   k_smem = p_smem + CHAINS * P_BUFS * P_BYTES, v_smem = k_smem + K_STAGES * K_STAGE;
     const uint32_t bars = v_smem + V_STAGES * V_STAGE;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile uint32_t* tmem_slot =
@@ -131,6 +138,24 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     const int kbase0 = (lo / BN) * BN;
     const int n_tiles = (hi - kbase0) / BN + 1;
 
+    // a softmax thread's half of its row of Q is asked for before the set-up below, so
+    // that the two latencies overlap
+    uint4 q_regs[HD / 16];
+    if (warp >= 2) {
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        const int row = row0 + q * 32 + lane;
+        const bool live = row < rows;
+        const int ti = live ? row / P.group : 0, g = live ? row - ti * P.group : 0;
+        const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
+        const __nv_bfloat16* src =
+            P.qkv + (size_t)(tok0 + ti) * row_w + (size_t)(kvh * P.group + g) * HD;
+#pragma unroll
+        for (int i = 0; i < HD / 16; ++i) {
+            q_regs[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (live) q_regs[i] = *reinterpret_cast<const uint4*>(src + (half * (HD / 16) + i) * 8);
+        }
+    }
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < K_STAGES; ++s) {
             mbar_init(bar(B_K_FULL + s), 1);
@@ -142,13 +167,13 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         }
         for (int s = 0; s < 2 * CHAINS; ++s) {
             mbar_init(bar(B_S_FULL + s), 1);
-            mbar_init(bar(B_S_EMPTY + s), 128);
+            mbar_init(bar(B_S_EMPTY + s), SOFTMAX_THREADS);
         }
-        for (int c = 0; c < CHAINS; ++c) {
-            mbar_init(bar(B_P_FULL + c), 128);
+        for (int c = 0; c < P_BUFS * CHAINS; ++c) {
+            mbar_init(bar(B_P_FULL + c), SOFTMAX_THREADS);
             mbar_init(bar(B_P_EMPTY + c), 1);
         }
-        mbar_init(bar(B_Q_FULL), 128 * CHAINS);
+        mbar_init(bar(B_Q_FULL), SOFTMAX_THREADS);
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -256,7 +281,8 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                         timed_out = true;
                         break;
                     }
-                    if (!mbar_wait(bar(B_P_FULL + c), j & 1)) {
+                    const int pb = j % P_BUFS;
+                    if (!mbar_wait(bar(B_P_FULL + P_BUFS * c + pb), (j / P_BUFS) & 1)) {
                         timed_out = true;
                         break;
                     }
@@ -269,96 +295,112 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
                     for (int kk = 0; kk < BN / 16; ++kk)
                         umma(tmem + COL_O + c * HD,
-                             umma_desc(p_smem + c * P_BYTES + (kk >> 2) * BLOCK + (kk & 3) * 32),
+                             umma_desc(p_smem + (P_BUFS * c + pb) * P_BYTES + (kk >> 2) * BLOCK +
+                                       (kk & 3) * 32),
                              umma_desc_mn(v_src + kk * 16 * 128, KBLOCK), idesc_o,
                              (j | kk) ? 1u : 0u);
-                    umma_commit(bar(B_P_EMPTY + c));           // P_c is free, O_c holds tile j
+                    umma_commit(bar(B_P_EMPTY + P_BUFS * c + pb));   // this P is free, O holds tile j
                 }
                 umma_commit(bar(B_V_EMPTY + (j % V_STAGES)));  // the values of tile j are done with
             }
         }
     } else {
         // ------------------------------------------------- softmax, correction, epilogue
+        // Warps w and w + 4 own the same 32 rows (TMEM lanes of quarter w % 4); the first
+        // takes keys 0..63 of a tile, the second keys 64..127, and of O and of Q each
+        // half of the columns.  A scheduler thus has two warps to issue from.  The pair
+        // meets once a tile (named barrier) to agree on the row maximum.
         const int q = warp & 3;
-        const int c = (warp - 2) >> 2;                         // which chain
-        const int row_in = q * 32 + lane;                      // row of the chain = TMEM lane
-        const int row = row0 + c * 128 + row_in;
-        const uint32_t q_mine = q_smem + c * Q_BYTES, p_mine = p_smem + c * P_BYTES;
-        const int b_s_full = B_S_FULL + 2 * c, b_s_empty = B_S_EMPTY + 2 * c;
-        const int b_p_full = B_P_FULL + c, b_p_empty = B_P_EMPTY + c;
-        const uint32_t col_s = COL_S + 2 * c * BN, col_o = COL_O + c * HD;
+        const int half = (warp - 2) >> 2;                      // which half of the keys
+        const int row_in = q * 32 + lane;                      // row of the tile = TMEM lane
+        const int row = row0 + row_in;
+        constexpr int HB = BN / 2;                             // keys of a half
+        constexpr int HO = HD / 2;                             // columns of O of a half
         const bool live = row < rows;
         const int ti = live ? row / P.group : 0, g = live ? row - ti * P.group : 0;
         const int pos = live ? pos0 + ti : -1;
         const int lo_row = P.window > 0 ? pos - P.window + 1 : 0;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;\n" ::"r"(1 + q) : "memory"); };
 
-        // this thread's row of Q into shared memory, in the operand layout
+        // this thread's half of its row of Q into shared memory, in the operand layout
         {
-            const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
-            const __nv_bfloat16* src =
-                P.qkv + (size_t)(tok0 + ti) * row_w + (size_t)(kvh * P.group + g) * HD;
 #pragma unroll
-            for (int ch = 0; ch < HD / 8; ++ch) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (live) v = *reinterpret_cast<const uint4*>(src + ch * 8);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(swz(q_mine, row_in, ch)),
-                             "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            for (int i = 0; i < HD / 16; ++i) {
+                const uint4 v = q_regs[i];
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
+                             ::"r"(swz(q_smem, row_in, half * (HD / 16) + i)),
+                               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
             }
             fence_proxy_async();
             mbar_arrive(bar(B_Q_FULL));
         }
 
-        float m_used = -INFINITY, l = 0.f;
+        float m_used = -INFINITY, l = 0.f;                     // l: the sum over this half's keys
         for (int j = 0; j < n_tiles && !timed_out; ++j) {
             const int sb = j & 1;
-            const int kbase = kbase0 + j * BN;
-            if (!mbar_wait(bar(b_s_full + sb), (j >> 1) & 1)) {
+            const int kbase = kbase0 + j * BN + half * HB;     // first key of this half
+            if (!mbar_wait(bar(B_S_FULL + sb), (j >> 1) & 1)) {
                 timed_out = true;
                 break;
             }
             tc_fence_after();
-            const uint32_t s_addr = tmem + lane_base + col_s + sb * BN;
-            // the whole row of scores into registers, scaled to the log2 domain; a key
-            // needs a mask only on the diagonal tiles and at a window's edge
-            float sc[BN];
+            const uint32_t s_addr = tmem + lane_base + COL_S + sb * BN + half * HB;
+            // this half of the row of raw scores into registers (the scale to the log2
+            // domain is folded into the exponent's multiply-add); a key needs a mask only
+            // on the diagonal tiles and at a window's edge
+            float sc[HB];
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < HB; c0 += 32) {
                 uint32_t a[16], b[16];
                 tmem_ld16(s_addr + c0, a);
                 tmem_ld16(s_addr + c0 + 16, b);
                 tmem_ld_wait();
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
-                    sc[c0 + e] = __uint_as_float(a[e]) * P.scale_log2;
-                    sc[c0 + 16 + e] = __uint_as_float(b[e]) * P.scale_log2;
+                    sc[c0 + e] = __uint_as_float(a[e]);
+                    sc[c0 + 16 + e] = __uint_as_float(b[e]);
                 }
             }
-            const bool masked = kbase + BN - 1 > pos || kbase < lo_row;
+            // the scores are in registers: the tile after next may overwrite them
+            tc_fence_before();
+            mbar_arrive(bar(B_S_EMPTY + sb));
+            const bool masked = kbase + HB - 1 > pos || kbase < lo_row;
             if (__any_sync(0xffffffffu, masked)) {
 #pragma unroll
-                for (int e = 0; e < BN; ++e) {
+                for (int e = 0; e < HB; ++e) {
                     const int jj = kbase + e;
                     if (jj > pos || jj < lo_row) sc[e] = -INFINITY;
                 }
             }
-            float m_tile = -INFINITY;
+            // eight running maxima, then their maximum: no chain of dependent steps
+            float mx[8];
 #pragma unroll
-            for (int e = 0; e < BN; ++e) m_tile = fmaxf(m_tile, sc[e]);
-            // P of the previous tile must have been consumed, and O must be at rest
-            if (j > 0 && !mbar_wait(bar(b_p_empty), (j - 1) & 1)) {
-                timed_out = true;
-                break;
-            }
-            tc_fence_after();
+            for (int e = 0; e < 8; ++e) mx[e] = sc[e];
+#pragma unroll
+            for (int e = 8; e < HB; ++e) mx[e & 7] = fmaxf(mx[e & 7], sc[e]);
+            const float m_half = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                       fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) *
+                                 P.scale_log2;    // the scale is positive
+            // both halves' maxima: the row's maximum over the tile (slots alternate
+            // with the tile, so one meeting a tile is enough)
+            row_max[sb][half][row_in] = m_half;
+            pair_sync();
+            const float m_tile = fmaxf(row_max[sb][0][row_in], row_max[sb][1][row_in]);
             const bool grow = m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > m_used);
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? m_tile : m_used;
                 const float cf = (grow && m_used != -INFINITY) ? fast_exp2(m_used - m_new) : 1.0f;
                 if (j > 0) {
-                    const uint32_t o_addr = tmem + lane_base + col_o;
+                    // O must be at rest: the product of the tile before has to be done
+                    if (!mbar_wait(bar(B_P_EMPTY + (j - 1) % P_BUFS), ((j - 1) / P_BUFS) & 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t o_addr = tmem + lane_base + COL_O + half * HO;
 #pragma unroll
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                    for (int c0 = 0; c0 < HO; c0 += 32) {
                         uint32_t v[16], w[16];
                         tmem_ld16(o_addr + c0, v);
                         tmem_ld16(o_addr + c0 + 16, w);
@@ -376,48 +418,63 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                 l *= cf;
                 m_used = m_new;
             }
+            // this tile's P buffer was last read by the product of the tile two before
+            const int pb = j % P_BUFS;
+            if (j >= P_BUFS && !mbar_wait(bar(B_P_EMPTY + pb), ((j / P_BUFS) & 1) ^ 1)) {
+                timed_out = true;
+                break;
+            }
             // probabilities, their sum, and P as the next product's operand
-            const float base_m = m_used == -INFINITY ? 0.f : m_used;
-            float sum = 0.f;
+            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};             // four running sums
 #pragma unroll
-            for (int ch = 0; ch < BN / 8; ++ch) {
+            for (int ch = 0; ch < HB / 8; ++ch) {
                 uint32_t pk[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    const float p0 = fast_exp2(sc[ch * 8 + 2 * u] - base_m);
-                    const float p1 = fast_exp2(sc[ch * 8 + 2 * u + 1] - base_m);
-                    sum += p0 + p1;
+                    const float p0 = fast_exp2(fmaf(sc[ch * 8 + 2 * u], P.scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(sc[ch * 8 + 2 * u + 1], P.scale_log2, neg_m));
+                    part[u] += p0 + p1;
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     pk[u] = *reinterpret_cast<uint32_t*>(&h);
                 }
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
-                             ::"r"(swz(p_mine, row_in, ch)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
-                               "r"(pk[3]) : "memory");
+                             ::"r"(swz(p_smem + pb * P_BYTES, row_in, half * (HB / 8) + ch)),
+                               "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
             }
-            l += sum;
-            tc_fence_before();
+            l += (part[0] + part[1]) + (part[2] + part[3]);
+            tc_fence_before();                 // a rescaled O is in place before the product adds to it
             fence_proxy_async();
-            mbar_arrive(bar(b_s_empty + sb));
-            mbar_arrive(bar(b_p_full));
+            mbar_arrive(bar(B_P_FULL + pb));
         }
-        // the last P V, then the row's output
-        if (!timed_out && n_tiles > 0 && !mbar_wait(bar(b_p_empty), (n_tiles - 1) & 1))
+        // the row's sum is the two halves' sums (first half first); they meet in the
+        // slots the last tile did not use
+        float (*row_sum)[128] = row_max[n_tiles & 1];
+        row_sum[half][row_in] = l;
+        pair_sync();
+        const float l_row = row_sum[0][row_in] + row_sum[1][row_in];
+        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+        // the last P V (the products end in the order they were issued), then the row's output
+        if (!timed_out && n_tiles > 0 &&
+            !mbar_wait(bar(B_P_EMPTY + (n_tiles - 1) % P_BUFS), ((n_tiles - 1) / P_BUFS) & 1))
             timed_out = true;
         tc_fence_after();
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
         __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
-                             (size_t)(kvh * P.group + g) * HD;
+                             (size_t)(kvh * P.group + g) * HD + half * HO;
+        uint32_t ov[HO / 16][16];                  // all loads under way, one wait
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 16) {
-            uint32_t v[16];
-            tmem_ld16(tmem + lane_base + col_o + c0, v);
-            tmem_ld_wait();
-            if (live) {
+        for (int c0 = 0; c0 < HO; c0 += 16)
+            tmem_ld16(tmem + lane_base + COL_O + half * HO + c0, ov[c0 / 16]);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+            for (int c0 = 0; c0 < HO; c0 += 16) {
                 uint32_t w[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * e]) * inv,
-                                                             __uint_as_float(v[2 * e + 1]) * inv);
+                    __nv_bfloat162 h =
+                        __floats2bfloat162_rn(__uint_as_float(ov[c0 / 16][2 * e]) * inv,
+                                              __uint_as_float(ov[c0 / 16][2 * e + 1]) * inv);
                     w[e] = *reinterpret_cast<uint32_t*>(&h);
                 }
                 *reinterpret_cast<uint4*>(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
