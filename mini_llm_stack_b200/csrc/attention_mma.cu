@@ -494,26 +494,55 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
 
 // out[unit] = sum_s w_s part_o[s, unit] with w_s = 2^(lse_s - max lse) normalised.
 // One block per (token, head), one thread per element of the head.
+constexpr int MAX_SPLITS = 256;
 __global__ void attention_merge_kernel(const Params P) {
     chain_release();
-    chain_wait();
+    __shared__ float weight[MAX_SPLITS];
+    __shared__ float total;
     const int t = blockIdx.x, h = blockIdx.y;
-    // only the requests the split kernel took have partial results
+    // only the requests the split kernel took have partial results (the step's index
+    // arrays were copied before its first kernel began)
     int r = 0;
     while (r + 1 < P.n_req && P.cu_q[r + 1] <= t) ++r;
-    if (!is_small(P.cu_q[r + 1] - P.cu_q[r], P.group)) return;
+    const bool mine = is_small(P.cu_q[r + 1] - P.cu_q[r], P.group);
+    chain_wait();
+    if (!mine) return;
     const size_t units = (size_t)P.n_tokens * P.n_heads;
     const size_t unit = (size_t)t * P.n_heads + h;
-    float m = -INFINITY;
-    for (int s = 0; s < P.n_split; ++s) m = fmaxf(m, P.part_lse[s * units + unit]);
+    // the parts' weights 2^(lse - max), by the first warp: all loads under way together
+    if (threadIdx.x < 32) {
+        float lse[MAX_SPLITS / 32];
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            const int s = threadIdx.x + 32 * i;
+            lse[i] = s < P.n_split ? P.part_lse[s * units + unit] : -INFINITY;
+            m = fmaxf(m, lse[i]);
+        }
+        m = warp_max(m);
+        float wsum = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; ++i) {
+            const int s = threadIdx.x + 32 * i;
+            const float w = (m == -INFINITY || s >= P.n_split) ? 0.f : fast_exp2(lse[i] - m);
+            if (s < P.n_split) weight[s] = w;
+            wsum += w;
+        }
+        wsum = warp_sum(wsum);
+        if (threadIdx.x == 0) total = wsum;
+    }
+    __syncthreads();
+    const float wsum = total;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float wsum = 0.f, acc = 0.f;
-        if (m != -INFINITY) {
-            for (int s = 0; s < P.n_split; ++s) {
-                const float w = fast_exp2(P.part_lse[s * units + unit] - m);
-                wsum += w;
-                acc += w * P.part_o[(s * units + unit) * HD + d];
-            }
+        float acc = 0.f;
+        for (int s0 = 0; s0 < P.n_split; s0 += 8) {
+            float o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < P.n_split) o[j] = P.part_o[((s0 + j) * units + unit) * HD + d];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < P.n_split) acc += weight[s0 + j] * o[j];
         }
         P.out[unit * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
     }
@@ -1113,7 +1142,8 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
                               int n_split, float* part_o, float* part_lse, long long pool_pages,
                               int* status, int use_tma, cudaStream_t stream) {
     if (n_tokens <= 0 || n_req <= 0) return 0;
-    if (n_heads % n_kv || n_split < 1 || (n_split > 1 && (!part_o || !part_lse)))
+    if (n_heads % n_kv || n_split < 1 || n_split > MAX_SPLITS ||
+        (n_split > 1 && (!part_o || !part_lse)))
         return MLS_ERR_UNSUPPORTED;
     static bool configured = false;
     if (!configured) {
@@ -1196,7 +1226,8 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
         int rc = launch_status();
         if (rc) return rc;
         if (n_split > 1) {
-            MLS_LAUNCH((attention_merge_kernel), dim3(n_tokens, n_heads), dim3(HD < 128 ? HD : 128),
+            MLS_LAUNCH((attention_merge_kernel), dim3(n_tokens, n_heads),
+                       dim3(HD < 32 ? 32 : (HD < 128 ? HD : 128)),
                        0, stream, P);
             rc = launch_status();
             if (rc) return rc;
