@@ -24,6 +24,7 @@ class EngineOptions:
     dtype: str | None = None          # None: the model folder's own dtype
     device: str = "cuda:0"
     cuda_graphs: bool = True          # replay pure-decode steps from a graph
+    launch_ahead: bool = True         # start the next decode step before the host has this one's tokens
 
     def __post_init__(self):
         for k in ("num_blocks", "block_size", "max_batch", "max_tokens_per_step",

@@ -12,7 +12,7 @@ import time
 
 from ..sampling.sampler import Sampler, uniform_for
 from .batch import Entry
-from .request import Request
+from .request import RUNNING, Request
 from .runner import ModelRunner
 from .scheduler import Planned, Scheduler, StepPlan
 
@@ -20,7 +20,7 @@ from .scheduler import Planned, Scheduler, StepPlan
 class Engine:
     def __init__(self, model, num_blocks: int = 256, block_size: int = 16, max_batch: int = 16,
                  max_tokens_per_step: int = 2048, chunk_size: int = 2048,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, launch_ahead: bool = True):
         self.model = model
         self.runner = ModelRunner(model, num_blocks=num_blocks, block_size=block_size,
                                   max_requests=max_batch, cuda_graphs=cuda_graphs)
@@ -31,6 +31,8 @@ class Engine:
         self.sampler = Sampler(model.runtime, max_rows=max_batch)
         self._next_id = 0
         self._prepared = None                # (plan, arrays) of a step prepared ahead
+        self.launch_ahead = launch_ahead
+        self._ahead = None                   # (plan, logits) of a step already on the device
         self.step_tokens: list = []
 
     @classmethod
@@ -38,7 +40,8 @@ class Engine:
         """An engine from an ``EngineOptions`` record."""
         return cls(model, num_blocks=options.num_blocks, block_size=options.block_size,
                    max_batch=options.max_batch, max_tokens_per_step=options.max_tokens_per_step,
-                   chunk_size=options.chunk_size, cuda_graphs=options.cuda_graphs)
+                   chunk_size=options.chunk_size, cuda_graphs=options.cuda_graphs,
+                   launch_ahead=options.launch_ahead)
 
     # the reference's attribute names
     @property
@@ -70,36 +73,61 @@ class Engine:
 
         While the device computes a step of single decoded tokens, the host lays
         out the next step's arrays (they depend on lengths and pages, not on the
-        tokens being sampled); if nothing changed by the time the tokens are
-        known, the next step starts without planning or building.
+        tokens being sampled).  With ``launch_ahead`` that next step is put on the
+        device at once, reading its token ids where the sampler writes them, before
+        the host has read them: the device never waits for the host between steps
+        of decoding.  A request that turns out to have ended with the token just
+        sampled has one row in the step launched ahead, which nobody reads (a row
+        does not depend on the rest of its batch).  Without ``launch_ahead`` the
+        prepared step waits for the tokens and starts without planning or building
+        if nothing changed meanwhile.
         """
         if not self.scheduler.has_work():
+            self._ahead = None
             return False
-        ahead = self._take_prepared()
-        if ahead is not None:
-            plan, prepared = ahead
-            logits = self.runner.step_prepared(
-                prepared, [p.request.generated[-1] for p in plan.entries])
-        else:
-            plan = self.scheduler.plan()
-            entries = []
-            for p in plan.entries:
-                r = p.request
-                toks = r.token_slice(r.num_computed, p.n_tokens)
-                entries.append(Entry(r.req_id, toks, [p.n_tokens - 1] if p.wants_logits else []))
-            logits = self.runner.step(entries)
+        plan = logits = rows = None
+        if self._ahead is not None:
+            ahead_plan, ahead_logits = self._ahead
+            self._ahead = None
+            keep = [i for i, p in enumerate(ahead_plan.entries) if p.request.state == RUNNING]
+            if keep:
+                plan = StepPlan(entries=[ahead_plan.entries[i] for i in keep])
+                logits = ahead_logits
+                if len(keep) != len(ahead_plan.entries):
+                    rows = keep
+        if plan is None:
+            ahead = self._take_prepared()
+            if ahead is not None:
+                plan, prepared = ahead
+                logits = self.runner.step_prepared(
+                    prepared, [p.request.generated[-1] for p in plan.entries])
+            else:
+                plan = self.scheduler.plan()
+                entries = []
+                for p in plan.entries:
+                    r = p.request
+                    toks = r.token_slice(r.num_computed, p.n_tokens)
+                    entries.append(Entry(r.req_id, toks,
+                                         [p.n_tokens - 1] if p.wants_logits else []))
+                logits = self.runner.step(entries)
         sampled = {}
+        nxt = None
         if logits is not None:
+            if rows is not None:                     # the rows of the requests still running
+                logits = logits[rows].contiguous()
             wanting = [p.request for p in plan.entries if p.wants_logits]
             temps = [r.temperature for r in wanting]
             us = [uniform_for(r.seed, r.req_id, len(r.generated)) if r.temperature > 0 else 0.0
                   for r in wanting]
             n = self.sampler.launch(logits, temps, us)
             nxt = self._prepare_next(plan)          # host work under the device's
+            if nxt is not None and self.launch_ahead:
+                next_plan, prepared = nxt
+                self._ahead = (next_plan, self.runner.step_prepared(
+                    prepared, None, device_tokens=self.sampler.device_tokens(n)))
+                nxt = None
             toks = self.sampler.finish(n)
             sampled = {r.req_id: t for r, t in zip(wanting, toks)}
-        else:
-            nxt = None
         done = self.scheduler.complete(plan, sampled)
         self._prepared = None if done else nxt
         self.step_tokens.append(plan.n_tokens)

@@ -122,10 +122,14 @@ class ModelRunner:
         return logits
 
     @torch.no_grad()
-    def step_prepared(self, prepared, token_ids: list):
+    def step_prepared(self, prepared, token_ids, device_tokens=None):
         """``step`` for a batch of single tokens whose arrays were prepared ahead
-        (``BatchBuilder.prepare``) and whose token ids are known only now."""
+        (``BatchBuilder.prepare``) and whose token ids are known only now: as a list
+        on the host, or (``device_tokens``, int32 on the device, in the order of the
+        entries) still on their way from the sampler."""
         ctx = self.builder.submit(prepared, token_ids)
+        if device_tokens is not None:
+            ctx.token_ids.copy_(device_tokens[:ctx.n_tokens])
         if self.cuda_graphs and ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens:
             logits = self._decode_from_graph(ctx)
         else:

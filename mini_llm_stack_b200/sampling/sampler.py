@@ -36,6 +36,7 @@ class Sampler:
     def __init__(self, runtime, max_rows: int = 64):
         self.runtime = runtime
         self._cap = 0
+        self._copied = torch.cuda.Event()        # the tokens of the last launch are on the host
         self._grow(max_rows)
 
     def _grow(self, n: int) -> None:
@@ -65,9 +66,15 @@ class Sampler:
         else:
             ops.sample(logits, None, None, self._out)
         self._out_host[:n].copy_(self._out[:n], non_blocking=True)
+        self._copied.record(torch.cuda.current_stream(self.runtime.device))
         return n
 
+    def device_tokens(self, n: int):
+        """The tokens of the last ``launch`` where the kernel wrote them (int32 [n] on
+        the device): a next step may read them there before the host has them."""
+        return self._out[:n]
+
     def finish(self, n: int) -> list:
-        """Wait for the tokens of the last ``launch``."""
-        torch.cuda.current_stream(self.runtime.device).synchronize()
+        """Wait for the tokens of the last ``launch`` (not for work queued after it)."""
+        self._copied.synchronize()
         return self._out_host[:n].tolist()

@@ -106,3 +106,42 @@ def test_command_line_chat(folders, tmp_path):
         capture_output=True, text=True, cwd=ROOT, timeout=900)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert proc.stdout.startswith("'kernel ' -> ")
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_steps_launched_ahead_give_the_same_tokens(folders, temperature):
+    """The next decode step starts before the host has read this step's tokens.  Requests
+    that end on an end token (known one step late), by count, and one that arrives while
+    a step is already on its way must come out as without launching ahead."""
+    folder, cfg, w = folders[("B", "float32")]
+    prompts = [tokens_for(97, n, 70 + n) for n in (3, 14, 29, 8)]
+    free_run = [P.plain_generate(w, cfg, p, 40, temperature=temperature, seed=9, request=i)
+                for i, p in enumerate(prompts)]
+    # end tokens that do occur: request 0 ends early, request 2 in the middle
+    eos = {0: free_run[0][5], 2: free_run[2][17]}
+    news = {0: 40, 1: 23, 2: 40, 3: 40}
+
+    def run(launch_ahead):
+        llm = LLM.from_folder(folder, dtype="float32", num_blocks=64, block_size=8, max_batch=4,
+                              launch_ahead=launch_ahead)
+        eng = llm.engine
+        reqs = [eng.submit(prompts[i], news[i], eos.get(i), temperature, 9) for i in range(3)]
+        late = None
+        while eng.step():
+            if late is None and eng.steps == 6:           # a step may be on the device already
+                late = eng.submit(prompts[3], news[3], None, temperature, 9)
+        assert late is not None and not eng.step()
+        eng.model.runtime.ops.check_status()
+        eng.cache.check()
+        assert eng.cache.num_free_pages() == 64
+        return [list(r.generated) for r in reqs + [late]], eng
+
+    ahead, eng = run(True)
+    plain, _ = run(False)
+    assert ahead == plain
+    for i, got in enumerate(ahead):
+        want = free_run[i][:news[i]]
+        if i in eos:
+            want = want[:want.index(eos[i]) + 1]
+        assert got == want
+    assert eng.launch_ahead
