@@ -501,6 +501,23 @@ def test_far_key_at_the_full_context_with_the_8b_heads(rts, far, ctx, q_len):
     assert (got[visible] - mark).abs().max().item() < 3e-2
 
 
+@pytest.mark.parametrize("far, ctx, q_len", [(55, 4096, 1), (2049, 4096, 700), (4000, 4096, 97)])
+def test_far_key_with_heads_of_64(rts, far, ctx, q_len):
+    """The same with 32 query heads over 8 kv heads of 64 (the Llama-3.2-1B geometry): the
+    tcgen05 kernel and the split kernel compiled for the other head size they take."""
+    case = AttnCase(rts[torch.bfloat16], 32, 8, 64, 16, [ctx], [q_len], seed=8)
+    q, k, v = case.q[0], case.k[0], case.v[0]
+    k.mul_(0.05)
+    direction = torch.ones(64, dtype=q.dtype, device=DEV)
+    q[:] = direction * 4
+    k[:, far] = direction * 4                      # 16 * 64 / 8 = 128 above all others
+    got = case.run()
+    rts[torch.bfloat16].ops.check_status()
+    mark = v[:, far].float().cpu().repeat_interleave(4, dim=0).reshape(1, -1)
+    visible = torch.arange(ctx - q_len, ctx) >= far
+    assert (got[visible] - mark).abs().max().item() < 3e-2
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window, ctx, q_len", [(10, 50, 1), (16, 64, 1), (40, 200, 30), (33, 100, 100),
                                                 (64, 1000, 1), (5, 300, 17)])
