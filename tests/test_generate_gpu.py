@@ -145,3 +145,49 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, temperature):
             want = want[:want.index(eos[i]) + 1]
         assert got == want
     assert eng.launch_ahead
+
+
+def test_many_requests_arriving_ending_and_giving_way_with_steps_launched_ahead(folders):
+    """Forty requests with random lengths, end tokens and arrival steps over so few pages
+    that some give way: launching ahead must not change a token, lose a page or a slot."""
+    import random
+    folder, cfg, w = folders[("C", "float32")]
+    rng = random.Random(11)
+    jobs = []
+    for i in range(40):
+        prompt = tokens_for(301, rng.randint(1, 60), 200 + i)
+        jobs.append(dict(prompt=prompt, new=rng.randint(1, 40), eos=rng.choice([None, None, rng.randrange(301)]),
+                         at=rng.randint(0, 120), temperature=rng.choice([0.0, 0.8])))
+
+    def run(launch_ahead):
+        llm = LLM.from_folder(folder, dtype="float32", num_blocks=20, max_batch=6, chunk_size=24,
+                              max_tokens_per_step=48, launch_ahead=launch_ahead)
+        eng = llm.engine
+        reqs = [None] * len(jobs)
+        step = 0
+        while True:
+            for i, j in enumerate(jobs):
+                if j["at"] == step:
+                    eng._next_id = i
+                    reqs[i] = eng.submit(j["prompt"], j["new"], j["eos"], j["temperature"], 4)
+            more = eng.step()
+            step += 1
+            if not more and all(r is not None for r in reqs):
+                break
+            assert step < 5000
+        eng.model.runtime.ops.check_status()
+        eng.cache.check()
+        assert eng.cache.num_free_pages() == 20 and eng.cache.slots.num_free == 6
+        return [list(r.generated) for r in reqs], eng.scheduler.preemptions
+
+    ahead, pre_a = run(True)
+    plain, pre_p = run(False)
+    assert ahead == plain
+    assert pre_a > 0 and pre_p > 0                        # pages did run out
+    for i in (0, 7, 19, 33):
+        j = jobs[i]
+        want = P.plain_generate(w, cfg, j["prompt"], j["new"], temperature=j["temperature"], seed=4,
+                                request=i)
+        if j["eos"] is not None and j["eos"] in want:
+            want = want[:want.index(j["eos"]) + 1]
+        assert ahead[i] == want
