@@ -131,6 +131,18 @@ static __device__ __forceinline__ void sum_parts4_of(const float* __restrict__ b
     }
 }
 
+// Streaming multiprocessors of the current device (148 on a B200), asked once.
+static inline int sm_count() {
+    static const int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+            v = 148;
+        return v;
+    }();
+    return n;
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch.  A kernel started with `launch_chained` may

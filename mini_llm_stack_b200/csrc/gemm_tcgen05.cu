@@ -398,7 +398,7 @@ int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
     if (!operand_map(a, p.mm, p.k, BM, &amap) || !operand_map(b, p.nn, p.k, BN, &bmap))
         return MLS_ERR_TENSOR_MAP;
     const long long tiles = (long long)((p.mm + BM - 1) / BM) * ((p.nn + BN - 1) / BN) * p.splits;
-    const long long most = 148LL * ctas_per_sm;
+    const long long most = (long long)sm_count() * ctas_per_sm;
     const int grid = (int)(tiles < most ? tiles : most);
     MLS_LAUNCH((gemm_tcgen05_kernel<BN, STAGES>), dim3(grid), dim3(THREADS), L::TOTAL, stream, p,
                amap, bmap);
@@ -443,7 +443,7 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
         if (rc || splits == 1 || out == nullptr) return rc;
         const size_t total = (size_t)m * p.ld_out;
         int blocks = (int)((total + 255) / 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks > sm_count() * 8) blocks = sm_count() * 8;
         MLS_LAUNCH((splitk_sum_kernel), dim3(blocks), dim3(256), 0, stream, partial, out, out_f32,
                    m, n, splits, epilogue);
         return launch_status();

@@ -350,7 +350,7 @@ MLS_API int mls_add_rmsnorm(float* x, const void* delta, int delta_dtype, const 
         const int esize = delta ? (delta_dtype == MLS_BF16 ? 2 : 4) : 0;
         const int half_bytes = (STREAM_ROWS * d * (4 + esize) + 127) / 128 * 128;
         if (vec == 1 && threads >= 32 * STREAM_ROWS && d % 8 == 0 && rows == nullptr &&
-            delta_parts == 1 && n_rows >= 2 * 148 && 2 * half_bytes <= 200 * 1024) {
+            delta_parts == 1 && n_rows >= 2 * sm_count() && 2 * half_bytes <= 200 * 1024) {
             static bool configured = false;
             if (!configured) {
                 cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_stream_kernel,
@@ -359,14 +359,14 @@ MLS_API int mls_add_rmsnorm(float* x, const void* delta, int delta_dtype, const 
                 if (e != cudaSuccess) return (int)e;
                 configured = true;
             }
-            MLS_LAUNCH((add_rmsnorm_stream_kernel), dim3(148), dim3(threads),
+            MLS_LAUNCH((add_rmsnorm_stream_kernel), dim3(sm_count()), dim3(threads),
                        (size_t)2 * half_bytes, stream, x, delta, delta_dtype, w, w_dtype, eps, h,
                        h_dtype, n_rows, d, status);
             return launch_status();
         }
         // as many blocks as run at the same time; each takes its rows in turn
         const int vv = vec <= 1 ? 1 : (vec <= 2 ? 2 : 4);
-        int resident = 148 * (1024 / threads < 16 ? 1024 / threads : 16);
+        int resident = sm_count() * (1024 / threads < 16 ? 1024 / threads : 16);
         const int blocks = n_rows < resident ? n_rows : resident;
         if (vv == 1)
             MLS_LAUNCH((add_rmsnorm_vec_kernel<1>), dim3(blocks), dim3(threads), 0, stream, x,

@@ -112,6 +112,7 @@ class Ops:
                 "this engine runs on a CUDA device only (sm_100a kernels); "
                 f"device {device!r} is not one and there is no CPU path")
         self.act_dtype = act_dtype
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._libs: list = []                    # every kernel library in use
         self._chained = True                     # what the libraries were last told
         core = self._load("core")
@@ -288,7 +289,7 @@ class Ops:
         as fit at the same time, at least 256 of K each."""
         tiles = (n + 127) // 128
         kblocks = (k + 63) // 64
-        splits = max(1, min(kblocks // 4, (2 * 148) // tiles))
+        splits = max(1, min(kblocks // 4, (2 * self.sm_count) // tiles))
         per = -(-kblocks // splits)
         return -(-kblocks // per)
 
@@ -428,7 +429,7 @@ class Ops:
             n_split = 1
             if n_small:
                 longest = max(c for c, s in zip(step.ctx_lens, small) if s)
-                n_split = self.split_for(n_small, longest, n_kv)
+                n_split = self.split_for(n_small, longest, n_kv, self.sm_count)
             plan = (n_tiles, 1 if n_small else 0, n_split, n_tiles_tc)
             step.attn_tiles[key] = plan
         return plan
@@ -447,10 +448,10 @@ class Ops:
         return out
 
     @staticmethod
-    def split_for(n_small: int, longest: int, n_kv: int) -> int:
+    def split_for(n_small: int, longest: int, n_kv: int, sm_count: int = 148) -> int:
         """Context splits for ``n_small`` decoding requests of up to ``longest`` keys.
 
-        Two CTAs of the split kernel fit an SM, so 296 run at a time; the cost of
+        Two CTAs of the split kernel fit an SM, so 296 run at a time on a B200; the cost of
         a choice is its number of such waves times the 64-key tiles a CTA walks
         (plus six tiles' worth of start-up), plus the merge kernel's time, which
         grows with the number of parts (measured at batch 1: 16 parts beat 32).
@@ -459,7 +460,7 @@ class Ops:
         forced = os.environ.get("MLS_B200_SPLITS")
         if forced:
             return max(1, min(int(forced), max(1, longest // 64)))
-        slots = 2 * 148
+        slots = 2 * sm_count
         pairs = max(1, n_small * n_kv)
         tiles = -(-longest // 64)
         best, best_cost = 1, None
