@@ -42,7 +42,6 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
-    import numpy as np
     import torch
 
     from .batch import Entry

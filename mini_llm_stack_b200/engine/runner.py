@@ -20,7 +20,7 @@ from ..config.registry import build_model, config_from_folder
 from ..ops.kernels import Runtime
 from ..weights.loader import device_dtype, load_tensors
 from ..weights.random_init import random_tensors
-from .batch import BatchBuilder, Entry
+from .batch import BatchBuilder
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 

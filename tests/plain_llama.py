@@ -14,7 +14,6 @@ path (sums, softmax, norms and rotations stay in float32 either way).
 
 from __future__ import annotations
 
-import math
 
 import torch
 

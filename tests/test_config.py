@@ -8,7 +8,7 @@ from mini_llm_stack_b200.config import (ConfigError, DenseLlamaConfig, build_mod
                                         config_from_dict, config_from_folder,
                                         lookup_architecture, register_architecture,
                                         unregister_architecture, write_config_json)
-from tiny_configs import CONFIGS, TINY_A, TINY_B, TINY_C
+from tiny_configs import CONFIGS, TINY_A, TINY_C
 
 
 def test_reference_keys_and_derived_sizes():

@@ -1,12 +1,10 @@
 """Generation through the entry points on the GPU, against the plain implementation."""
 
-import json
 import subprocess
 import sys
 from pathlib import Path
 
 import pytest
-import torch
 
 import plain_llama as P
 from engine_helpers import RND, make_folder, tokens_for

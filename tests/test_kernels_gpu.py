@@ -9,7 +9,7 @@ import plain_llama as P
 from mini_llm_stack_b200.cache.manager import CacheManager
 from mini_llm_stack_b200.engine.batch import BatchBuilder, Entry
 from mini_llm_stack_b200.ops.kernels import KernelError, Runtime
-from mini_llm_stack_b200.parts.base import CacheHandle, PagedKV
+from mini_llm_stack_b200.parts.base import PagedKV
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"

@@ -8,7 +8,6 @@ configurations.
 """
 
 import json
-import os
 import subprocess
 import sys
 from pathlib import Path

@@ -3,7 +3,7 @@
 import pytest
 
 from mini_llm_stack_b200.cache.manager import CacheManager
-from mini_llm_stack_b200.engine.request import FINISHED, RUNNING, WAITING, Request
+from mini_llm_stack_b200.engine.request import FINISHED, Request
 from mini_llm_stack_b200.engine.scheduler import Scheduler, SchedulerError
 from mini_llm_stack_b200.parts.base import PagedKV
 
