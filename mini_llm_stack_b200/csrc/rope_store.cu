@@ -17,7 +17,7 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                   const int* __restrict__ slot_map, T* __restrict__ k_pool,
                                   T* __restrict__ v_pool, int n_heads, int n_kv, int hd,
-                                  int block_size, int max_pos, long long pool_slots, int writes,
+                                  int block_size, int max_pos, int pool_slots, int writes,
                                   int* status) {
     chain_release();
     chain_wait();
@@ -32,13 +32,13 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     const float* sr = sin_t + (size_t)pos * half;
     T* row = qkv + (size_t)t * (n_heads + 2 * n_kv) * hd;
 
-    long long slot = writes ? (long long)slot_map[t] : 0;
+    const int slot = writes ? slot_map[t] : 0;      // 32-bit: the divisions below are per thread
     bool slot_ok = slot >= 0 && slot < pool_slots;
     if (writes && !slot_ok) {
         if (threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_SLOT);
     }
-    const long long page = slot / block_size, off = slot % block_size;
-    const long long n_pages = pool_slots / block_size;
+    const int page = slot / block_size, off = slot - page * block_size;
+    const int n_pages = pool_slots / block_size;
 
     const int rot_heads = n_heads + (writes ? n_kv : 0);
     for (int u = threadIdx.x; u < rot_heads * half; u += blockDim.x) {
@@ -103,12 +103,13 @@ template <> struct Vec16<__nv_bfloat16> {
 // The same work as rope_store_kernel for head sizes whose halves are whole 16-byte
 // chunks; one thread rotates one chunk pair of one head, or copies one chunk of v.
 template <typename T>
-__global__ void __launch_bounds__(512, 3) rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void __launch_bounds__(512, 3)
+rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                       const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t,
                                       const int* __restrict__ slot_map, T* __restrict__ k_pool,
                                       T* __restrict__ v_pool, int n_heads, int n_kv, int hd,
-                                      int block_size, int max_pos, long long pool_slots, int writes,
+                                      int block_size, int max_pos, int pool_slots, int writes,
                                       int* status) {
     chain_release();
     constexpr int N = Vec16<T>::N;
@@ -121,10 +122,10 @@ __global__ void __launch_bounds__(512, 3) rope_store_vec_kernel(T* __restrict__ 
     const float* cr = cos_t + (size_t)pos * half;
     const float* sr = sin_t + (size_t)pos * half;
     T* row = qkv + (size_t)t * (n_heads + 2 * n_kv) * hd;
-    long long slot = writes ? (long long)slot_map[t] : 0;
+    const int slot = writes ? slot_map[t] : 0;      // 32-bit: the divisions below are per thread
     const bool slot_ok = slot >= 0 && slot < pool_slots;
-    const long long page = slot / block_size, off = slot % block_size;
-    const long long n_pages = pool_slots / block_size;
+    const int page = slot / block_size, off = slot - page * block_size;
+    const int n_pages = pool_slots / block_size;
     chain_wait();
     if (threadIdx.x == 0 && status) {
         if (bad_pos) atomicOr(status, MLS_STATUS_BAD_POSITION);
@@ -200,7 +201,7 @@ rope_store_parts_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__
                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                         const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, int n_heads, int n_kv, int hd,
-                        int block_size, int max_pos, long long pool_slots, int writes,
+                        int block_size, int max_pos, int pool_slots, int writes,
                         const float* __restrict__ parts, int n_parts, size_t part_stride,
                         int* status) {
     chain_release();
@@ -212,10 +213,10 @@ rope_store_parts_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__
     const float* cr = cos_t + (size_t)pos * half;
     const float* sr = sin_t + (size_t)pos * half;
     const size_t width = (size_t)(n_heads + 2 * n_kv) * hd;
-    long long slot = writes ? (long long)slot_map[t] : 0;
+    const int slot = writes ? slot_map[t] : 0;      // 32-bit: the divisions below are per thread
     const bool slot_ok = slot >= 0 && slot < pool_slots;
-    const long long page = slot / block_size, off = slot % block_size;
-    const long long n_pages = pool_slots / block_size;
+    const int page = slot / block_size, off = slot - page * block_size;
+    const int n_pages = pool_slots / block_size;
     const int rot_units = (n_heads + (writes ? n_kv : 0)) * qph;
     const int v_units = writes ? n_kv * (hd / 4) : 0;
     const int per_block = (rot_units + v_units + gridDim.y - 1) / gridDim.y;
@@ -277,6 +278,8 @@ MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const flo
                            cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 2) return MLS_ERR_UNSUPPORTED;
+    // slots are int32
+    if (pool_slots > 0x7fffffffLL || block_size <= 0) return MLS_ERR_UNSUPPORTED;
     const int vec_n = dtype == MLS_BF16 ? 8 : 4;
     if (parts) {
         // rows still in parts: bfloat16 activations, whole float4s in every part
@@ -288,7 +291,7 @@ MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const flo
         MLS_LAUNCH((rope_store_parts_kernel), dim3(n_tokens, per_token), dim3(PARTS_THREADS), 0,
                    stream, (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map,
                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_heads, n_kv, hd, block_size,
-                   max_pos, pool_slots, writes, parts, n_parts, (size_t)part_stride, status);
+                   max_pos, (int)pool_slots, writes, parts, n_parts, (size_t)part_stride, status);
         return launch_status();
     }
     if ((hd / 2) % vec_n == 0) {
@@ -299,12 +302,12 @@ MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const flo
             MLS_LAUNCH((rope_store_vec_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(vthreads), 0,
                        stream, (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map,
                        (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, n_heads, n_kv, hd,
-                       block_size, max_pos, pool_slots, writes, status);
+                       block_size, max_pos, (int)pool_slots, writes, status);
         else
             MLS_LAUNCH((rope_store_vec_kernel<float>), dim3(n_tokens), dim3(vthreads), 0, stream,
                        (float*)qkv, positions, cos_t, sin_t, slot_map, (float*)k_pool,
-                       (float*)v_pool, n_heads, n_kv, hd, block_size, max_pos, pool_slots, writes,
-                       status);
+                       (float*)v_pool, n_heads, n_kv, hd, block_size, max_pos, (int)pool_slots,
+                       writes, status);
         return launch_status();
     }
     const int work = (n_heads + n_kv) * hd / 2;
@@ -313,11 +316,11 @@ MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const flo
     if (dtype == MLS_BF16)
         MLS_LAUNCH((rope_store_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(threads), 0, stream,
                    (__nv_bfloat16*)qkv, positions, cos_t, sin_t, slot_map, (__nv_bfloat16*)k_pool,
-                   (__nv_bfloat16*)v_pool, n_heads, n_kv, hd, block_size, max_pos, pool_slots,
+                   (__nv_bfloat16*)v_pool, n_heads, n_kv, hd, block_size, max_pos, (int)pool_slots,
                    writes, status);
     else
         MLS_LAUNCH((rope_store_kernel<float>), dim3(n_tokens), dim3(threads), 0, stream,
                    (float*)qkv, positions, cos_t, sin_t, slot_map, (float*)k_pool, (float*)v_pool,
-                   n_heads, n_kv, hd, block_size, max_pos, pool_slots, writes, status);
+                   n_heads, n_kv, hd, block_size, max_pos, (int)pool_slots, writes, status);
     return launch_status();
 }
