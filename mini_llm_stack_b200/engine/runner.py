@@ -32,7 +32,7 @@ def load_model(folder, dtype: str | None = None, device="cuda:0"):
     runtime = Runtime(device, run_dtype)
     model = build_model(config)
     tensors = load_tensors(folder, model.tensor_specs(), model.tied_names(), run_dtype,
-                           runtime.device)
+                           runtime.device, aliases=model.name_aliases())
     model.bind(tensors, runtime)
     return model
 

@@ -19,6 +19,34 @@ from .norm import RMSNorm
 from .position import RotaryPosition
 
 
+# The spellings Llama model folders commonly use for the reference's state_dict names
+# (same tensors, same layouts: [out, in] matrices, rotate-half pairing of q and k).
+_FOLDER_NAMES = {
+    "embed.weight": "model.embed_tokens.weight",
+    "final_norm.weight": "model.norm.weight",
+    "attn_norm.weight": "input_layernorm.weight",
+    "mlp_norm.weight": "post_attention_layernorm.weight",
+    "attn.wq.weight": "self_attn.q_proj.weight",
+    "attn.wk.weight": "self_attn.k_proj.weight",
+    "attn.wv.weight": "self_attn.v_proj.weight",
+    "attn.wo.weight": "self_attn.o_proj.weight",
+    "mlp.w_gate.weight": "mlp.gate_proj.weight",
+    "mlp.w_up.weight": "mlp.up_proj.weight",
+    "mlp.w_down.weight": "mlp.down_proj.weight",
+}
+
+
+def folder_names(name: str) -> list:
+    """Other names a weight file may give the tensor the reference calls ``name``."""
+    if name in _FOLDER_NAMES:
+        return [_FOLDER_NAMES[name]]
+    parts = name.split(".", 2)
+    if (len(parts) == 3 and parts[0] == "blocks" and parts[1].isdigit()
+            and parts[2] in _FOLDER_NAMES):
+        return [f"model.layers.{parts[1]}.{_FOLDER_NAMES[parts[2]]}"]
+    return []
+
+
 def build_llama_dense(cfg: DenseLlamaConfig) -> ComposedModel:
     embedding = TokenEmbedding(cfg.vocab_size, cfg.d_model)
     blocks = []
@@ -41,7 +69,7 @@ def build_llama_dense(cfg: DenseLlamaConfig) -> ComposedModel:
     head = OutputHead(cfg.vocab_size, cfg.d_model,
                       tied_to=embedding if cfg.tie_embeddings else None)
     return ComposedModel(cfg, embedding, blocks, calls,
-                         RMSNorm(cfg.d_model, cfg.norm_eps), head)
+                         RMSNorm(cfg.d_model, cfg.norm_eps), head, aliases=folder_names)
 
 
 register_architecture("llama_dense", DenseLlamaConfig, build_llama_dense)

@@ -73,8 +73,9 @@ class ComposedModel:
 
     def __init__(self, config, embedding: TokenEmbedding, blocks: list,
                  calls: list, final_norm, head: OutputHead,
-                 names=("embed", "blocks", "final_norm", "lm_head")):
+                 names=("embed", "blocks", "final_norm", "lm_head"), aliases=None):
         self.config = config
+        self._aliases = aliases          # callable: tensor name -> other names a file may use
         self.embedding, self.blocks, self.calls = embedding, list(blocks), list(calls)
         self.final_norm, self.head = final_norm, head
         self.names = tuple(names)
@@ -101,6 +102,14 @@ class ComposedModel:
         out.update({f"{f}.{n}": s for n, s in self.final_norm.tensor_specs().items()})
         out.update({f"{h}.{n}": s for n, s in self.head.tensor_specs().items()})
         return out
+
+    def name_aliases(self) -> dict:
+        """For the names of ``tensor_specs`` and ``tied_names``: other spellings a
+        weight file may use for the same tensor (the architecture's builder says which)."""
+        if self._aliases is None:
+            return {}
+        names = list(self.tensor_specs()) + list(self.tied_names())
+        return {n: a for n in names if (a := list(self._aliases(n)))}
 
     def tied_names(self) -> dict:
         """Names a file may hold although the model takes them from another."""

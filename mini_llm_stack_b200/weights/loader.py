@@ -13,13 +13,64 @@ int32.  In a float32 run every floating tensor is float32.
 
 from __future__ import annotations
 
+import json
 from pathlib import Path
 
 import torch
 
-from .safetensors_io import SafetensorsFile
+from .safetensors_io import SafetensorsFile, SafetensorsFormatError
 
 WEIGHT_FILE = "model.safetensors"
+INDEX_FILE = "model.safetensors.index.json"     # {"weight_map": {tensor name: file name}}
+
+
+class WeightShards:
+    """The tensors of a folder whose weights are spread over several safetensors
+    files, named by ``model.safetensors.index.json``: one ``entries`` table and one
+    ``read``, like a single file."""
+
+    def __init__(self, folder: Path):
+        self.path = folder / INDEX_FILE
+        try:
+            weight_map = json.loads(self.path.read_text())["weight_map"]
+        except (json.JSONDecodeError, KeyError, TypeError) as exc:
+            raise SafetensorsFormatError(f"{self.path}: no \"weight_map\" table") from exc
+        self._files = {}
+        self.entries = {}
+        try:
+            for name, fname in weight_map.items():
+                if fname not in self._files:
+                    self._files[fname] = SafetensorsFile(folder / fname)
+                f = self._files[fname]
+                if name not in f.entries:
+                    raise SafetensorsFormatError(
+                        f"{self.path}: says {name!r} is in {fname}, which does not hold it")
+                self.entries[name] = f.entries[name]
+            self._where = {n: self._files[f] for n, f in weight_map.items()}
+        except Exception:
+            self.close()
+            raise
+
+    def read(self, name: str) -> torch.Tensor:
+        return self._where[name].read(name)
+
+    def close(self) -> None:
+        for f in self._files.values():
+            f.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+def open_weights(folder):
+    """The folder's ``model.safetensors``, or the files its index names."""
+    folder = Path(folder)
+    if (folder / WEIGHT_FILE).is_file() or not (folder / INDEX_FILE).is_file():
+        return SafetensorsFile(folder / WEIGHT_FILE)
+    return WeightShards(folder)
 
 
 class WeightError(ValueError):
@@ -83,22 +134,43 @@ def check_against_specs(path, entries: dict, specs: dict, tied: dict) -> None:
         raise WeightError(path, missing, unexpected, wrong, other)
 
 
+def resolve_names(entries: dict, wanted, aliases: dict) -> dict:
+    """``{name the model uses: name the file uses}`` for the wanted names the file has
+    under their own name or, failing that, under one of their ``aliases``."""
+    stored = {}
+    for name in wanted:
+        for cand in (name, *aliases.get(name, ())):
+            if cand in entries:
+                stored[name] = cand
+                break
+    return stored
+
+
 def load_tensors(folder, specs: dict, tied: dict, run_dtype: torch.dtype,
-                 device) -> dict:
-    """Read every tensor in ``specs`` from ``folder`` onto ``device``."""
-    path = Path(folder) / WEIGHT_FILE
-    with SafetensorsFile(path) as f:
-        check_against_specs(path, f.entries, specs, tied)
+                 device, aliases: dict | None = None) -> dict:
+    """Read every tensor in ``specs`` from ``folder`` onto ``device``.
+
+    ``aliases`` maps a name to other spellings the file may use for it; errors name
+    tensors as the model does.
+    """
+    with open_weights(folder) as f:
+        path = f.path
+        stored = resolve_names(f.entries, list(specs) + list(tied), aliases or {})
+        used = set(stored.values())
+        # the file's tensors under the model's names; what the model has no name for stays
+        entries = {n: f.entries[s] for n, s in stored.items()}
+        entries.update({n: e for n, e in f.entries.items() if n not in used and n not in entries})
+        check_against_specs(path, entries, specs, tied)
         out = {}
         for name, spec in specs.items():
-            t = f.read(name)
+            t = f.read(stored[name])
             out[name] = t.to(device=device,
                              dtype=device_dtype(t.dtype, spec.kind, run_dtype))
         mismatched = []
         for name, target in tied.items():
-            if name in f.entries:
-                a = f.read(name)
-                b = f.read(target)
+            if name in stored:
+                a = f.read(stored[name])
+                b = f.read(stored[target])
                 if not torch.equal(a, b.to(a.dtype)):
                     mismatched.append(
                         f"{name}: the model ties it to {target}, but the file "

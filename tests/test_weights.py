@@ -89,6 +89,67 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert word in text
 
 
+def test_a_file_may_use_the_usual_folder_spellings_of_the_names(tmp_path):
+    cfg = _folder(tmp_path, TINY_B)
+    path = str(tmp_path / "model.safetensors")
+    m = build_model(cfg)
+    # copies: the file is written over below, and tensors read from it are views of its mapping
+    want = {n: t.clone() for n, t in load_tensors(tmp_path, m.tensor_specs(), m.tied_names(),
+                                                  torch.float32, "cpu").items()}
+    aliases = m.name_aliases()
+    assert aliases["blocks.2.attn.wk.weight"] == ["model.layers.2.self_attn.k_proj.weight"]
+    assert aliases["embed.weight"] == ["model.embed_tokens.weight"] and "lm_head.weight" not in aliases
+    w = {n: t.clone() for n, t in load_file(path).items()}
+    renamed = {aliases.get(n, [n])[0]: t.clone() for n, t in w.items()}
+    assert set(renamed).isdisjoint(set(w) - {"lm_head.weight"})
+    save_file(renamed, path)
+    with pytest.raises(WeightError):                       # not without the table
+        load_tensors(tmp_path, m.tensor_specs(), m.tied_names(), torch.float32, "cpu")
+    got = load_tensors(tmp_path, m.tensor_specs(), m.tied_names(), torch.float32, "cpu",
+                       aliases=aliases)
+    assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+    # errors speak the model's names; a leftover tensor keeps the file's
+    renamed["model.layers.0.mlp.up_proj.weight"] = torch.zeros(3, 3)
+    del renamed["model.norm.weight"]
+    renamed["model.layers.7.rotary.inv_freq"] = torch.zeros(4)
+    save_file(renamed, path)
+    with pytest.raises(WeightError) as err:
+        load_tensors(tmp_path, m.tensor_specs(), m.tied_names(), torch.float32, "cpu",
+                     aliases=aliases)
+    e = err.value
+    assert e.missing == ["final_norm.weight"] and e.unexpected == ["model.layers.7.rotary.inv_freq"]
+    assert [n for n, _, _ in e.wrong_shape] == ["blocks.0.mlp.w_up.weight"]
+    # a name of the model's own wins over its other spelling
+    both = dict(w)
+    both["model.embed_tokens.weight"] = torch.zeros_like(w["embed.weight"])
+    save_file(both, path)
+    with pytest.raises(WeightError) as err:
+        load_tensors(tmp_path, m.tensor_specs(), m.tied_names(), torch.float32, "cpu",
+                     aliases=aliases)
+    assert err.value.unexpected == ["model.embed_tokens.weight"]
+
+
+def test_weights_spread_over_several_files_with_an_index(tmp_path):
+    cfg = _folder(tmp_path, TINY_A, "bfloat16")
+    m = build_model(cfg)
+    want = load_tensors(tmp_path, m.tensor_specs(), m.tied_names(), torch.bfloat16, "cpu")
+    names = sorted(want)
+    parts = {"model-00001-of-00002.safetensors": names[::2],
+             "model-00002-of-00002.safetensors": names[1::2]}
+    for fname, own in parts.items():
+        save_file({n: want[n].clone() for n in own}, str(tmp_path / fname))
+    (tmp_path / "model.safetensors").unlink()
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"metadata": {}, "weight_map": {n: f for f, own in parts.items() for n in own}}))
+    got = load_tensors(tmp_path, m.tensor_specs(), m.tied_names(), torch.bfloat16, "cpu")
+    assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+    # an index that names a tensor its file does not hold
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {names[0]: "model-00002-of-00002.safetensors"}}))
+    with pytest.raises(SafetensorsFormatError, match="does not hold"):
+        load_tensors(tmp_path, m.tensor_specs(), m.tied_names(), torch.bfloat16, "cpu")
+
+
 def test_tied_head_in_the_file_is_accepted_only_if_equal(tmp_path):
     cfg = _folder(tmp_path, TINY_A)
     path = str(tmp_path / "model.safetensors")
