@@ -3,8 +3,10 @@
 Each request alone and whole; most of it in one step and the last 32 tokens one
 by one; in portions of changing size down to two tokens; and mixed, up to four
 live requests, portions of some beside decoded tokens of others, with so few
-pages that they are used again.  In float32 and in bfloat16, for three tiny
-configurations.
+pages that they are used again.  In float32 and in bfloat16, for five tiny
+configurations: three with small heads, and two (D, E) whose heads of 64 and 128
+send the bfloat16 runs through the tcgen05 / TMA attention kernels, the fused
+gate-up product and the weight-major product that large models use.
 """
 
 import json
@@ -21,8 +23,10 @@ from engine_helpers import (Replayer, assert_close, make_folder, plain_logits, t
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 DTYPES = ["float32", "bfloat16"]
-KEYS = ["A", "B", "C"]
-LENGTHS = {"A": [5, 17, 33, 150], "B": [1, 9, 40, 77, 300], "C": [3, 64, 131, 260]}
+KEYS = ["A", "B", "C", "D", "E"]
+LENGTHS = {"A": [5, 17, 33, 150], "B": [1, 9, 40, 77, 300], "C": [3, 64, 131, 260],
+           "D": [2, 63, 129, 300, 515], "E": [1, 31, 130, 257, 600]}
+BLOCKS = {"A": 24, "B": 24, "C": 24, "D": 40, "E": 40}      # pages for one request
 
 
 @pytest.fixture(scope="module")
@@ -35,7 +39,7 @@ def folders(tmp_path_factory):
 @pytest.mark.parametrize("key", KEYS)
 def test_each_request_alone_and_whole(folders, key, dtype):
     folder, cfg, w = folders[(key, dtype)]
-    rp = Replayer(folder, dtype, num_blocks=24)
+    rp = Replayer(folder, dtype, num_blocks=BLOCKS[key])
     for i, n in enumerate(LENGTHS[key]):
         toks = {i: tokens_for(cfg["vocab_size"], n, 100 + i)}
         rp.step([(i, n)], toks, end=[i])
@@ -47,9 +51,9 @@ def test_each_request_alone_and_whole(folders, key, dtype):
 @pytest.mark.parametrize("key", KEYS)
 def test_last_32_tokens_one_by_one(folders, key, dtype):
     folder, cfg, w = folders[(key, dtype)]
-    n = {"A": 180, "B": 333, "C": 250}[key]
+    n = {"A": 180, "B": 333, "C": 250, "D": 370, "E": 421}[key]
     toks = {"r": tokens_for(cfg["vocab_size"], n, 5)}
-    rp = Replayer(folder, dtype, num_blocks=24)
+    rp = Replayer(folder, dtype, num_blocks=BLOCKS[key])
     rp.step([("r", n - 32)], toks)
     for _ in range(32):
         rp.step([("r", 1)], toks)
@@ -62,22 +66,23 @@ def test_last_32_tokens_one_by_one(folders, key, dtype):
 def test_portions_of_changing_size(folders, key, dtype):
     folder, cfg, w = folders[(key, dtype)]
     sizes = [16, 7, 3, 2, 2, 5, 31, 2, 17, 64, 1, 2, 33, 9]
+    if key in "DE":                # portions of more than one 128-row tile, and a long tail
+        sizes = sizes + [130, 2, 70, 3, 129]
     n = sum(sizes)
     toks = {"r": tokens_for(cfg["vocab_size"], n, 6)}
-    rp = Replayer(folder, dtype, num_blocks=16)
+    rp = Replayer(folder, dtype, num_blocks=BLOCKS[key])
     for s in sizes:
         rp.step([("r", s)], toks)
     assert_close(rp.logits("r"), plain_logits(w, cfg, toks["r"], dtype), dtype,
                  f"tiny-{key} {dtype} portions {sizes}")
 
 
-def mixed_schedule(lens):
+def mixed_schedule(lens, portion=(13, 2, 29, 5, 2, 40, 3, 16)):
     """Up to four live requests; portions of some beside single tokens of others;
     finished requests give their pages to later ones."""
     ids = list(range(len(lens)))
     fed = {i: 0 for i in ids}
     waiting, live, steps = list(ids), [], []
-    portion = [13, 2, 29, 5, 2, 40, 3, 16]
     k = 0
     while waiting or live:
         while waiting and len(live) < 4:
@@ -107,11 +112,17 @@ def mixed_schedule(lens):
 def test_mixed_with_pages_used_again(folders, key, dtype):
     folder, cfg, w = folders[(key, dtype)]
     lens = [70, 45, 9, 120, 33, 64, 17, 90, 2, 51]
+    num_blocks = 16
+    portion = (13, 2, 29, 5, 2, 40, 3, 16)
+    if key in "DE":                # longer requests, portions of several query tiles
+        lens = [200, 45, 9, 310, 33, 140, 17, 190, 2, 151]
+        num_blocks = 36
+        portion = (13, 2, 150, 5, 2, 40, 67, 16)
     toks = {i: tokens_for(cfg["vocab_size"], n, 40 + i) for i, n in enumerate(lens)}
-    steps = mixed_schedule(lens)
+    steps = mixed_schedule(lens, portion)
     # the pool holds what four live requests need at worst, rounded up to pages of
     # 16: far fewer pages than all requests together, so pages are used again
-    rp = Replayer(folder, dtype, num_blocks=16)
+    rp = Replayer(folder, dtype, num_blocks=num_blocks)
     seen = set()
     reused = False
     for step, end in steps:
@@ -124,7 +135,7 @@ def test_mixed_with_pages_used_again(folders, key, dtype):
             pass
         seen |= {p for r in rp.runner.cache.live() for p in rp.runner.cache.pages_of(r)}
     assert max(len(s) for s, _ in steps) == 4
-    assert sum(lens) > 16 * 16 and reused
+    assert sum(lens) > num_blocks * 16 and reused
     for i in toks:
         assert_close(rp.logits(i), plain_logits(w, cfg, toks[i], dtype), dtype,
                      f"tiny-{key} {dtype} mixed, request {i}")
