@@ -61,13 +61,15 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
-        self.rows, self.proc, self.thread = [], None, None
+    def __init__(self, gpu: str = "0"):
+        """``gpu``: what ``nvidia-smi -i`` takes: the UUID of the device in use (its
+        index inside this process says nothing on a machine with several GPUs)."""
+        self.rows, self.proc, self.thread, self.gpu = [], None, None, gpu
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                ["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.FIELDS}",
                  "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
@@ -102,6 +104,15 @@ class ClockSampler:
                 "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
 
 
+def device_uuid(torch) -> str:
+    """The UUID of cuda:0 of this process, in nvidia-smi's spelling ("0" if unknown)."""
+    try:
+        u = str(torch.cuda.get_device_properties(0).uuid)
+        return u if u.startswith("GPU-") else "GPU-" + u
+    except Exception:                              # noqa: BLE001 (older torch: no uuid)
+        return "0"
+
+
 def weight_bytes(cfg, layers: int) -> int:
     d, hd = cfg["d_model"], cfg["head_dim"]
     per_layer = ((cfg["n_heads"] + 2 * cfg["n_kv_heads"]) * hd * d + d * cfg["n_heads"] * hd
@@ -131,13 +142,15 @@ MODEL_7B = dict(architecture="llama_dense", vocab_size=32000, d_model=4096, n_la
                 dtype="bfloat16")
 
 
-def serve_workload(name: str) -> int:
+def serve_workload(name: str, short: bool = False) -> dict:
     """Requests through the scheduler: chunked prompts beside decoding requests.
 
     mixed_1b: 64 requests at once, prompts of 16..4096 tokens (log-uniform), 256 new
     tokens each, Llama-3.2-1B shape.  poisson_7b: 128 requests arriving as a Poisson
     process, prompts of 128..2048 tokens, 128..512 new tokens, Llama-2-7B shape, with
-    so few pages that requests are preempted and recomputed.
+    so few pages that requests are preempted and recomputed.  ``short``: a quarter of
+    the requests (and of the new tokens of mixed_1b), for the decode line's ``points``.
+    Returns the workload's line.
     """
     import random
 
@@ -152,13 +165,13 @@ def serve_workload(name: str) -> int:
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     if name == "mixed_1b":
-        raw, max_batch, budget, n_req = MODEL_1B, 64, 4096, 64
+        raw, max_batch, budget, n_req = MODEL_1B, 64, 4096, 16 if short else 64
         lens = [int(round(16 * (4096 / 16) ** rng.random())) for _ in range(n_req)]
-        outs = [256] * n_req
+        outs = [64 if short else 256] * n_req
         arrivals = [0.0] * n_req
         num_blocks = sum((a + b) // PAGE + 2 for a, b in zip(lens, outs))
     else:
-        raw, max_batch, budget, n_req = MODEL_7B, 64, 4096, 128
+        raw, max_batch, budget, n_req = MODEL_7B, 64, 4096, 32 if short else 128
         lens = [rng.randint(128, 2048) for _ in range(n_req)]
         outs = [rng.randint(128, 512) for _ in range(n_req)]
         t, arrivals = 0.0, []
@@ -210,12 +223,57 @@ def serve_workload(name: str) -> int:
         "preemptions": engine.scheduler.preemptions,
         "ttft_s": {"p50": round(ttft[len(ttft) // 2], 4), "p99": round(ttft[-2], 4)},
         "tpot_ms": {"p50": round(tpot[len(tpot) // 2] * 1e3, 3), "p99": round(tpot[-2] * 1e3, 3)},
-        "config": {"model": name, "layers": raw["n_layers"], "hidden": raw["d_model"],
+        "config": {"model": name, "device": torch.cuda.get_device_name(0),
+                   "layers": raw["n_layers"], "hidden": raw["d_model"],
                    "heads": raw["n_heads"], "kv_heads": raw["n_kv_heads"],
                    "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
                    "vocab": raw["vocab_size"], "max_batch": max_batch, "token_budget": budget,
                    "page_size": PAGE, "num_blocks": num_blocks},
     }
+    del engine, model
+    torch.cuda.empty_cache()
+    return line
+
+
+def correctness_gate() -> None:
+    """Nothing is timed before the engine has generated the right tokens: a tiny
+    random model in float32 and in bfloat16 against the plain implementation (the
+    reference's benchmarks are gated the same way: kaggle/kaggle_bench.py:46-54)."""
+    import contextlib
+    import io
+
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+
+    with contextlib.redirect_stdout(io.StringIO()):
+        entry.smoke()
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference through its own engine; nothing of this package."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("reference_arm",
+                                                  ROOT / "baseline" / "reference_arm.py")
+    arm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(arm)
+    if args.gpus != 1:
+        print(json.dumps(arm.unavailable("the reference's serving engine runs on one GPU")))
+        return 0
+    clocks = None
+    try:
+        import torch
+        if torch.cuda.is_available():
+            clocks = ClockSampler(device_uuid(torch))
+            clocks.start()
+    except Exception:                              # noqa: BLE001
+        clocks = None
+    line = arm.run(max(1, args.steps), max(3, args.warmup), args.batch, args.context,
+                   args.layers, not args.no_points)
+    if clocks is not None:
+        clocks.stop()
+        if "unavailable" not in line:
+            line["clocks"] = clocks.summary()
     print(json.dumps(line))
     return 0
 
@@ -283,6 +341,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=MODEL["max_seq_len"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--no-serving", action="store_true",
+                    help="skip the short serving workloads of points.served_*")
     ap.add_argument("--timeline", default=None, metavar="FILE",
                     help="instead of timing, record when each kernel of one decode step and of "
                          "one prefill step starts and ends (torch.profiler) and write the table "
@@ -293,19 +353,23 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "grenver/mini-llm-stack has no setup.py or pyproject.toml, so the "
-                          "offline pip install into baseline/_ref fails: not installable"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
-    if args.workload != "decode":
-        return serve_workload(args.workload)
-
     import torch
+
+    try:
+        correctness_gate()
+    except Exception as exc:                       # noqa: BLE001
+        print(f"bench.py: the correctness gate failed, nothing is timed: "
+              f"{type(exc).__name__}: {exc}", file=sys.stderr)
+        return 1
+    if args.workload != "decode":
+        print(json.dumps(serve_workload(args.workload)))
+        return 0
 
     sys.path.insert(0, str(ROOT))
     from mini_llm_stack_b200.config import config_from_dict
@@ -338,7 +402,7 @@ def main() -> int:
     if args.timeline:
         return write_timeline(args, torch, runner, cache, ops, ctx, rand_tokens, Entry)
 
-    clocks = ClockSampler()
+    clocks = ClockSampler(device_uuid(torch))
     clocks.start()
 
     def timed(fn, n_warm, n_timed):
@@ -352,6 +416,7 @@ def main() -> int:
             fn()
         e1.record()
         torch.cuda.synchronize()
+        ops.check_status()           # a kernel that refused its input or gave up a wait: no number
         return e0.elapsed_time(e1) / n_timed, (ops.launches - l0)
 
     # ------------------------------------------------------------------ prefill
@@ -371,9 +436,10 @@ def main() -> int:
                "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ------------------------------------------------------------------- decode
-    def decode_run(batch, n_warm, n_timed, end=None):
+    def decode_run(batch, n_warm, n_timed, end=None, temperature=0.0):
         """Device time of one decode step with ``batch`` requests that end at ``end``
-        (the context length by default)."""
+        (the context length by default); every row sampled at ``temperature`` if that
+        is positive, else by arg max."""
         start = (end or ctx) - (n_warm + n_timed)
         ids = [f"d{batch}_{i}" for i in range(batch)]
         for r in ids:
@@ -382,12 +448,16 @@ def main() -> int:
             cache.commit(r, start)              # the cache holds random keys and values
         last = [rand_tokens(1)[0] for _ in ids]
         out = torch.empty(batch, dtype=torch.int32, device=dev)
+        temps = us = None
+        if temperature > 0:
+            temps = torch.full((batch,), float(temperature), dtype=torch.float32, device=dev)
+            us = torch.rand(batch, dtype=torch.float32, device=dev)
 
         def one():
             e = [Entry(r, [t], [0]) for r, t in zip(ids, last)]
             runner.reserve(e)
             logits = runner.step(e)
-            ops.sample(logits, None, None, out)
+            ops.sample(logits, temps, us, out)
 
         ms, launches = timed(one, n_warm, n_timed)
         mean_ctx = start + n_warm + (n_timed + 1) / 2
@@ -406,6 +476,9 @@ def main() -> int:
         for b in (1, 64):
             pms, _, _ = decode_run(b, 3, max(8, steps // 4))
             points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        for b in (8, 64):                        # every row drawn at temperature 0.8
+            pms, _, _ = decode_run(b, 3, max(8, steps // 4), temperature=0.8)
+            points[f"decode_b{b}_temperature"] = round(b / pms * 1e3, 1)
         if ctx > 1024:                           # the same three batches early in a sequence
             for b in (1, 8, 64):
                 pms, _, _ = decode_run(b, 3, max(8, steps // 4), end=1024)
@@ -442,11 +515,21 @@ def main() -> int:
         engine.step()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    ops.check_status()
     e2e_tokens = sum(len(r.generated) for r in reqs) - n0
     assert len(engine.running) == args.batch and e2e_tokens == steps * args.batch
     h2d = runner.builder.last_bytes
     mark2 = clocks.mark()
     clocks.stop()
+    if not args.no_points and not args.no_serving:
+        # the other two workloads of the baseline's list, in short form, through the
+        # scheduler (their models need the memory this one holds)
+        del engine, runner, cache, model, reqs
+        torch.cuda.empty_cache()
+        for key, name in (("served_1b", "mixed_1b"), ("served_7b", "poisson_7b")):
+            w = serve_workload(name, short=True)
+            points[key] = w["value"]
+            points[key + "_preemptions"] = w["preemptions"]
 
     line = {
         "metric": "decode tok/s at batch 8, Llama-3-8B shape, context 8192 "
@@ -462,7 +545,8 @@ def main() -> int:
                    "vocab": raw["vocab_size"], "global_batch": args.batch, "seq_len": ctx,
                    "page_size": PAGE, "weights": "random N(0,0.02)", "parallelism": "none",
                    "l2": "inputs larger than L2 (weights and cache are read once a step)",
-                   "peaks": pk_src},
+                   "peaks": pk_src, "device": torch.cuda.get_device_name(0),
+                   "gate": "tiny model against the plain implementation: passed"},
         "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": int(launches),
