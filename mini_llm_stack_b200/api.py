@@ -42,19 +42,22 @@ def _tables(folder, vocab_size: int):
 
 
 def cmd_chat(args) -> int:
+    from .config.engine_options import EngineOptions
     from .config.model_config import ConfigError
     from .config.registry import config_from_dict
     from .engine.llm import LLM
 
-    opts = dict(num_blocks=args.num_blocks, block_size=args.block_size,
-                max_batch=args.max_batch, max_tokens_per_step=args.max_tokens_per_step,
-                chunk_size=args.chunk_size)
+    opts = EngineOptions(num_blocks=args.num_blocks, block_size=args.block_size,
+                         max_batch=args.max_batch,
+                         max_tokens_per_step=args.max_tokens_per_step,
+                         chunk_size=args.chunk_size, dtype=args.dtype, device=args.device,
+                         kv_dtype=args.kv_dtype, seed=args.sample_seed)
     if args.model:
-        llm = LLM.from_folder(args.model, dtype=args.dtype, **opts)
+        llm = LLM.from_folder(args.model, options=opts)
         folder = args.model
     elif args.random_weights:
         raw = json.loads(Path(args.random_weights).read_text())
-        llm = LLM.from_random(config_from_dict(raw), seed=args.seed, dtype=args.dtype, **opts)
+        llm = LLM.from_random(config_from_dict(raw), seed=args.seed, options=opts)
         folder = None
     else:
         raise SystemExit("give --model DIR or --random-weights CONFIG.json")
@@ -71,7 +74,7 @@ def cmd_chat(args) -> int:
         prompt = encode(args.prompt)
         shown = args.prompt
     out = llm.generate([prompt], max_new_tokens=args.max_new, temperature=args.temperature,
-                       seed=args.sample_seed, eos=args.eos)[0]
+                       eos=args.eos)[0]
     if args.token_ids:
         print(f"{shown!r} -> {','.join(str(t) for t in out)!r}")
     else:
@@ -104,6 +107,9 @@ def main(argv=None) -> int:
     c.add_argument("--sample-seed", type=int, default=0)
     c.add_argument("--eos", type=int, default=None)
     c.add_argument("--dtype", choices=["bfloat16", "float32"], default=None)
+    c.add_argument("--kv-dtype", choices=["bfloat16", "float32"], default=None,
+                   help="must equal the run's dtype (the cache is kept in it)")
+    c.add_argument("--device", default="cuda:0")
     c.add_argument("--num-blocks", type=int, default=512)     # serve/api.py:92
     c.add_argument("--block-size", type=int, default=16)
     c.add_argument("--max-batch", type=int, default=16)

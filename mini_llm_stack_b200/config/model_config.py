@@ -37,6 +37,25 @@ _ALIASES = {
     "torch_dtype": "dtype",
 }
 
+# Keys usual in Llama model folders that say nothing about the math of this decoder:
+# read and dropped.  Any other unknown key is an error.
+_IGNORED_KEYS = frozenset({
+    "model_type", "transformers_version", "bos_token_id", "eos_token_id", "pad_token_id",
+    "use_cache", "initializer_range", "pretraining_tp", "_name_or_path",
+})
+# Keys that would change the math: accepted only with the value that leaves it as it is.
+_NEUTRAL_VALUES = {
+    "rope_scaling": (None,),
+    "attention_bias": (False, None),
+    "mlp_bias": (False, None),
+    "hidden_act": ("silu", "swish", None),
+    "sliding_window": (None,),
+    "attention_dropout": (0, 0.0, None),
+}
+
+# Names model folders give this architecture (registered as aliases of ``llama_dense``).
+_FOLDER_ARCHITECTURES = ("LlamaForCausalLM",)
+
 _DTYPE_NAMES = {
     "bfloat16": "bfloat16", "bf16": "bfloat16",
     "float32": "float32", "fp32": "float32", "float": "float32",
@@ -148,10 +167,20 @@ class DenseLlamaConfig:
     def from_dict(cls, raw: dict) -> "DenseLlamaConfig":
         d: dict[str, Any] = {}
         for k, v in raw.items():
+            if k in _NEUTRAL_VALUES:
+                if v not in _NEUTRAL_VALUES[k]:
+                    raise ConfigError(
+                        f"config.json asks for {k} = {v!r}, which changes the model's math "
+                        f"and is not supported (only {list(_NEUTRAL_VALUES[k])!r} is)")
+                continue
+            if k in _IGNORED_KEYS:
+                continue
             d[_ALIASES.get(k, k)] = v
         if "architecture" not in d and isinstance(d.get("architectures"), list):
             d["architecture"] = d["architectures"][0]
         d.pop("architectures", None)
+        if d.get("architecture") in _FOLDER_ARCHITECTURES:
+            d["architecture"] = "llama_dense"
 
         if int(d.get("n_experts", 0) or 0) > 0:
             raise ConfigError(

@@ -12,6 +12,47 @@
 // slot = page * block + offset.
 #include "common.cuh"
 
+// What lies in a page past its owner's last token is whatever the page's previous owner
+// left there.  The attention kernels never count those slots, but the tensor-core ones
+// mask the scores, not the values: a probability of 0 times a leftover NaN or Inf would
+// still be NaN.  So the slots are cleared when a request enters a page: the token that
+// is the last of its request in this step zeroes the rest of its page (keys and values
+// of every kv head) if the page's first slot was written in this step too.  Pages are
+// owned by one request, so "the next token has the next slot" means "same request", and
+// "the token `off` places back has this page's first slot" means the page was entered
+// in this step.  Called by all threads of one block per token, after chain_wait().
+template <typename T>
+__device__ __forceinline__ void clear_page_tail(const int* __restrict__ slot_map, int t,
+                                                int n_tokens, int slot, int block_size,
+                                                int n_pages, int n_kv, int hd,
+                                                T* __restrict__ k_pool, T* __restrict__ v_pool) {
+    const int page = slot / block_size, off = slot - page * block_size;
+    const int rest = block_size - 1 - off;
+    if (rest <= 0) return;
+    if (t + 1 < n_tokens && slot_map[t + 1] == slot + 1) return;        // not the last one
+    if (off > 0 && (t - off < 0 || slot_map[t - off] != slot - off)) return;   // an older page
+    const size_t row_bytes = (size_t)hd * sizeof(T);
+    if (row_bytes % 16 == 0) {
+        const int chunks = (int)(row_bytes / 16) * rest;                 // per kv head and pool
+        for (int u = threadIdx.x; u < 2 * n_kv * chunks; u += blockDim.x) {
+            const int which = u / (n_kv * chunks), w = u - which * n_kv * chunks;
+            const int kvh = w / chunks, c = w - kvh * chunks;
+            T* base = (which ? v_pool : k_pool) +
+                      (((size_t)kvh * n_pages + page) * block_size + off + 1) * hd;
+            reinterpret_cast<uint4*>(base)[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    } else {
+        const int elems = hd * rest;
+        for (int u = threadIdx.x; u < 2 * n_kv * elems; u += blockDim.x) {
+            const int which = u / (n_kv * elems), w = u - which * n_kv * elems;
+            const int kvh = w / elems, c = w - kvh * elems;
+            T* base = (which ? v_pool : k_pool) +
+                      (((size_t)kvh * n_pages + page) * block_size + off + 1) * hd;
+            Elem<T>::store(base + c, 0.f);
+        }
+    }
+}
+
 template <typename T>
 __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -64,6 +105,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
             const int kvh = u / hd, i = u - kvh * hd;
             v_pool[(((size_t)kvh * n_pages + page) * block_size + off) * hd + i] = vsrc[u];
         }
+        clear_page_tail<T>(slot_map, t, gridDim.x, slot, block_size, n_pages, n_kv, hd, k_pool,
+                           v_pool);
     }
 }
 
@@ -172,6 +215,9 @@ rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                 v_pool + (((size_t)kvh * n_pages + page) * block_size + off) * hd + c * N) = raw;
         }
     }
+    if (writes && slot_ok)
+        clear_page_tail<T>(slot_map, t, gridDim.x, slot, block_size, n_pages, n_kv, hd, k_pool,
+                           v_pool);
 }
 
 // Four values rounded to bfloat16, as floats again / as the eight bytes to store.
@@ -268,6 +314,9 @@ rope_store_parts_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__
                 pack_bf16x4(x[0]);
         }
     }
+    if (writes && slot_ok && blockIdx.y == 0)
+        clear_page_tail<__nv_bfloat16>(slot_map, t, gridDim.x, slot, block_size, n_pages, n_kv, hd,
+                                       k_pool, v_pool);
 }
 
 MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const float* cos_t,

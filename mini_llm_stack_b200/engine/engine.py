@@ -20,8 +20,9 @@ from .scheduler import Planned, Scheduler, StepPlan
 class Engine:
     def __init__(self, model, num_blocks: int = 256, block_size: int = 16, max_batch: int = 16,
                  max_tokens_per_step: int = 2048, chunk_size: int = 2048,
-                 cuda_graphs: bool = True, launch_ahead: bool = True):
+                 cuda_graphs: bool = True, launch_ahead: bool = True, seed: int = 0):
         self.model = model
+        self.seed = int(seed)                # sampling seed of requests that bring none
         self.runner = ModelRunner(model, num_blocks=num_blocks, block_size=block_size,
                                   max_requests=max_batch, cuda_graphs=cuda_graphs)
         self.cache = self.runner.cache
@@ -37,11 +38,14 @@ class Engine:
 
     @classmethod
     def from_options(cls, model, options) -> "Engine":
-        """An engine from an ``EngineOptions`` record."""
+        """An engine from an ``EngineOptions`` record (whose ``dtype``, ``kv_dtype`` and
+        ``device`` must agree with how ``model`` was loaded)."""
+        rt = model.runtime
+        options.check_against(str(rt.act_dtype).replace("torch.", ""), rt.device)
         return cls(model, num_blocks=options.num_blocks, block_size=options.block_size,
                    max_batch=options.max_batch, max_tokens_per_step=options.max_tokens_per_step,
                    chunk_size=options.chunk_size, cuda_graphs=options.cuda_graphs,
-                   launch_ahead=options.launch_ahead)
+                   launch_ahead=options.launch_ahead, seed=options.seed)
 
     # the reference's attribute names
     @property
@@ -61,9 +65,9 @@ class Engine:
         return self.scheduler.steps
 
     def submit(self, prompt, max_new_tokens: int = 32, eos_token=None,
-               temperature: float = 0.0, seed: int = 0) -> Request:
+               temperature: float = 0.0, seed: int | None = None) -> Request:
         req = Request(self._next_id, list(prompt), int(max_new_tokens), eos_token,
-                      float(temperature), int(seed))
+                      float(temperature), self.seed if seed is None else int(seed))
         self.scheduler.add(req)
         self._next_id += 1
         return req
@@ -81,6 +85,13 @@ class Engine:
         does not depend on the rest of its batch).  Without ``launch_ahead`` the
         prepared step waits for the tokens and starts without planning or building
         if nothing changed meanwhile.
+
+        The kernels' status word comes back with the sampled tokens: a kernel that
+        refused its input (a token, position or slot outside its table) or gave up a
+        bounded wait raises ``KernelError`` in the step that ran it (the reference
+        raises inside the step too: serve/engine.py:242-244).  The lengths of that
+        step are committed by then and its rows are wrong, so the engine is not to be
+        used further after such an error.
         """
         if not self.scheduler.has_work():
             self._ahead = None

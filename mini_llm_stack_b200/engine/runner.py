@@ -112,7 +112,7 @@ class ModelRunner:
         the requests' lengths advance once, after the last layer.
         """
         ctx = self.builder.build(entries)
-        if self.cuda_graphs and ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens:
+        if self._may_replay(ctx):
             logits = self._decode_from_graph(ctx)
         else:
             logits = self.model.forward(ctx, self.handles)
@@ -130,7 +130,7 @@ class ModelRunner:
         ctx = self.builder.submit(prepared, token_ids)
         if device_tokens is not None:
             ctx.token_ids.copy_(device_tokens[:ctx.n_tokens])
-        if self.cuda_graphs and ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens:
+        if self._may_replay(ctx):
             logits = self._decode_from_graph(ctx)
         else:
             logits = self.model.forward(ctx, self.handles)
@@ -139,11 +139,18 @@ class ModelRunner:
         self.steps += 1
         return logits
 
+    def _may_replay(self, ctx) -> bool:
+        """A step of single decoded tokens, all wanted, of a model whose parts all
+        agree to be captured."""
+        return (self.cuda_graphs and ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens
+                and self.model.decode_capturable)
+
     def _decode_from_graph(self, ctx):
         """A step of single decoded tokens, replayed from a CUDA graph.
 
         Such a step launches the same kernels with the same arguments whenever
-        the number of requests and the cut of the context are the same; only
+        the number of requests and what the parts add to the key (the attention's
+        cut of the context) are the same; only
         the arrays the batch builder has just copied to the device differ, and
         they lie at the same addresses.  The first step of a kind runs eagerly
         (which sizes every buffer), the second is captured, later ones replay.
@@ -152,7 +159,7 @@ class ModelRunner:
         moved = (ops.generation, self.builder.generation)
         if moved != self._graphs.get("moved"):
             self._graphs = {"moved": moved}      # a buffer moved: the old graphs are stale
-        key = (ctx.n_requests, ops.decode_graph_key(ctx))
+        key = (ctx.n_requests, self.model.decode_graph_key(ctx))
         entry = self._graphs.get(key)
         if entry is None:
             self._graphs[key] = "warm"

@@ -130,8 +130,7 @@ class Ops:
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
-        self._tc_rows = 128                      # rows of a tile of the tcgen05 attention kernel
-        self._attention_shapes: set = set()      # (kv heads, group size) of the mixers
+        self._tc_rows: dict = {}                 # head size -> rows of a tile of the tcgen05 kernel
         self._scratch: dict = {}
         self._gemm = None
         self._parts_busy = False
@@ -175,15 +174,23 @@ class Ops:
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def check_status(self) -> None:
-        """Raise if a kernel met a token, position or slot outside its table."""
-        code = int(self.status.item())
+        """Raise if a kernel met a token, position or slot outside its table (waits
+        for the device)."""
+        self.raise_for_status(int(self.status.item()))
+
+    def raise_for_status(self, code: int) -> None:
+        """Raise for a status word already read (``code`` != 0), and clear it on the
+        device so that the next step starts clean."""
         if code:
             self.status.zero_()
             what = [n for b, n in ((1, "a token id outside the vocabulary"),
                                    (2, "a position outside the rotary table"),
                                    (4, "a cache slot outside the pool"),
-                                   (8, "a bounded wait inside a kernel ran out")) if code & b]
-            raise KernelError("a kernel refused its input: " + "; ".join(what))
+                                   (8, "a bounded wait inside a kernel ran out"),
+                                   (16, "shared memory of a kernel was not aligned"))
+                    if code & b]
+            raise KernelError("a kernel refused its input: " + ("; ".join(what) or
+                                                                f"status {code}"))
 
     # ------------------------------------------------------------------ kernels
     def embed(self, token_ids, table, x, vocab: int) -> None:
@@ -399,8 +406,6 @@ class Ops:
         """Make sure attention kernels for this head size exist, or say why not."""
         _need(hd % 16 == 0 and 16 <= hd <= 256,
               f"attention kernels take head sizes 16..256 in steps of 16, not {hd}")
-        if n_kv:
-            self._attention_shapes.add((n_kv, n_heads // n_kv))
         if self.act_dtype == torch.bfloat16 and hd not in self._attention_libs:
             lib = self._load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
@@ -410,69 +415,25 @@ class Ops:
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _LL, _P, _P])
             rows_fn = lib.mls_attention_tc_rows
             rows_fn.restype = ctypes.c_int
-            self._tc_rows = int(rows_fn()) or self._tc_rows
+            self._tc_rows[hd] = int(rows_fn()) or 128
             self._attention_libs[hd] = (fn, tc)
 
-    def _attention_plan(self, step, group: int, n_kv: int) -> tuple:
-        """(64-row tiles, any small request, context splits) for a step: requests
-        whose (token, head) rows of one kv head fit 16 rows go to the split
-        kernel, the context cut so that the GPU's SMs all have work."""
-        key = ("mma", group, n_kv)
-        plan = step.attn_tiles.get(key)
-        if plan is None:
-            small = [q * group <= 16 for q in step.q_lens]
-            n_tiles = sum((q * group + 63) // 64 for q, s in zip(step.q_lens, small) if not s)
-            rows = self._tc_rows
-            n_tiles_tc = sum((q * group + rows - 1) // rows
-                             for q, s in zip(step.q_lens, small) if not s)
-            n_small = sum(small)
-            n_split = 1
-            if n_small:
-                longest = max(c for c, s in zip(step.ctx_lens, small) if s)
-                n_split = self.split_for(n_small, longest, n_kv, self.sm_count)
-            plan = (n_tiles, 1 if n_small else 0, n_split, n_tiles_tc)
-            step.attn_tiles[key] = plan
-        return plan
-
-    def decode_graph_key(self, step) -> tuple:
-        """What, besides the number of requests, fixes the launches of a step of
-        single tokens: the number of context splits of the attention kernel."""
-        if self.act_dtype != torch.bfloat16 or self.attention_impl == "simt":
-            return ()
-        return tuple(sorted((k, v) for k, v in self._split_keys(step).items()))
-
-    def _split_keys(self, step) -> dict:
-        out = {}
-        for (n_kv, group) in self._attention_shapes:
-            out[(n_kv, group)] = self._attention_plan(step, group, n_kv)[2]
-        return out
-
-    @staticmethod
-    def split_for(n_small: int, longest: int, n_kv: int, sm_count: int = 148) -> int:
-        """Context splits for ``n_small`` decoding requests of up to ``longest`` keys.
-
-        Two CTAs of the split kernel fit an SM, so 296 run at a time on a B200; the cost of
-        a choice is its number of such waves times the 64-key tiles a CTA walks
-        (plus six tiles' worth of start-up), plus the merge kernel's time, which
-        grows with the number of parts (measured at batch 1: 16 parts beat 32).
-        The cheapest choice wins; a split is never shorter than 256 keys.
-        """
-        forced = os.environ.get("MLS_B200_SPLITS")
-        if forced:
-            return max(1, min(int(forced), max(1, longest // 64)))
-        slots = 2 * sm_count
-        pairs = max(1, n_small * n_kv)
-        tiles = -(-longest // 64)
-        best, best_cost = 1, None
-        for s in range(1, max(1, min(64, longest // 256)) + 1):
-            waves = -(-pairs * s // slots)
-            cost = waves * (-(-tiles // s) + 6) + (0.3 * s if s > 1 else 0.0)
-            if best_cost is None or cost < best_cost:
-                best, best_cost = s, cost
-        return best
+    def attention_facts(self, hd: int) -> dict:
+        """What a mixer needs to know of the attention kernels to plan a step's
+        launches: ``small_rows`` (requests whose (token, head) rows of one kv head are
+        at most this many go to the context-split kernel), ``tile_rows`` and
+        ``tc_rows`` (rows of a tile of the mma.sync and of the tcgen05 tile kernel),
+        ``split_slots`` (CTAs of the split kernel the GPU runs at a time: two an SM),
+        ``tensor_cores`` (False: the one-warp-per-row kernel runs, which needs no plan)."""
+        return {"small_rows": 16, "tile_rows": 64, "tc_rows": self._tc_rows.get(hd, 128),
+                "split_slots": 2 * self.sm_count,
+                "tensor_cores": self.act_dtype == torch.bfloat16 and self.attention_impl != "simt"}
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
-                        scale: float, window: int) -> None:
+                        scale: float, window: int, plan=None) -> None:
+        """Attention of the step's tokens over the pages.  ``plan`` (the mixer's, from
+        ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` tiles of the requests that are
+        not small, ``any_small``, ``n_split`` context splits for the small ones."""
         g = step.groups[cache.group]
         t = step.n_tokens
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
@@ -481,7 +442,9 @@ class Ops:
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
             fn, tc = fns
-            n_tiles, n_small, n_split, n_tiles_tc = self._attention_plan(step, n_heads // n_kv, n_kv)
+            _need(plan is not None, "attention: the tensor-core kernels need the mixer's plan")
+            n_tiles, n_small, n_split, n_tiles_tc = (plan.n_tiles, 1 if plan.any_small else 0,
+                                                     plan.n_split, plan.n_tiles_tc)
             if (n_tiles and hd in (64, 128) and g.block_size in (8, 16, 32, 64)
                     and self.attention_impl == "auto"):
                 # prompts and portions: the tcgen05 kernel; what is left for the call

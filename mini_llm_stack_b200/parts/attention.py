@@ -12,9 +12,44 @@ window w additionally hides keys ``j <= p - w`` from the query at position p.
 
 from __future__ import annotations
 
+import os
+from dataclasses import dataclass
+
 import torch
 
 from .base import CacheHandle, Mixer, PagedKV, StepContext, TensorSpec
+
+
+@dataclass(frozen=True)
+class AttentionPlan:
+    """How one step's attention is launched (for one shape of heads)."""
+    n_tiles: int          # tiles of the mma.sync tile kernel over the requests that are not small
+    n_tiles_tc: int       # tiles of the tcgen05 kernel over the same requests
+    any_small: bool       # some request has so few rows that the context-split kernel takes it
+    n_split: int          # parts the context of the small requests is cut into
+
+
+def context_splits(n_small: int, longest: int, n_kv: int, slots: int = 296) -> int:
+    """Context splits for ``n_small`` decoding requests of up to ``longest`` keys.
+
+    ``slots`` CTAs of the split kernel run at a time (two an SM: 296 on a B200); the cost
+    of a choice is its number of such waves times the 64-key tiles a CTA walks (plus six
+    tiles' worth of start-up), plus the merge kernel's time, which grows with the number
+    of parts (measured at batch 1: 16 parts beat 32).  The cheapest choice wins; a split
+    is never shorter than 256 keys.
+    """
+    forced = os.environ.get("MLS_B200_SPLITS")
+    if forced:
+        return max(1, min(int(forced), max(1, longest // 64)))
+    pairs = max(1, n_small * n_kv)
+    tiles = -(-longest // 64)
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(64, longest // 256)) + 1):
+        waves = -(-pairs * s // slots)
+        cost = waves * (-(-tiles // s) + 6) + (0.3 * s if s > 1 else 0.0)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 class GroupedQueryAttention(Mixer):
@@ -49,6 +84,50 @@ class GroupedQueryAttention(Mixer):
         self.wo = runtime.ops.prepare_weight(tensors["wo.weight"])
         self.position.bind({}, runtime)
         runtime.ops.require_attention(self.head_dim, self.n_heads, self.n_kv_heads)
+        self._facts = runtime.ops.attention_facts(self.head_dim)
+
+    # ---------------------------------------------------------- launch planning
+    @property
+    def decode_capturable(self) -> bool:
+        """Forward only launches kernels; the position part has to agree."""
+        return bool(getattr(self.position, "decode_capturable", False))
+
+    def plan(self, step: StepContext):
+        """This step's ``AttentionPlan`` (None where the kernel in use needs none).
+
+        Requests whose (token, head) rows of one kv head fit ``small_rows`` go to the
+        context-split kernel, their context cut so that all SMs have work; the others
+        are cut into tiles of rows.  Mixers with the same shape of heads share the
+        plan of a step."""
+        f = self._facts
+        if not f["tensor_cores"]:
+            return None
+        group = self.n_heads // self.n_kv_heads
+        key = ("gqa", group, self.n_kv_heads, self.head_dim)
+        plan = step.attn_tiles.get(key)
+        if plan is None:
+            small = [q * group <= f["small_rows"] for q in step.q_lens]
+            big = [q * group for q, s in zip(step.q_lens, small) if not s]
+            n_small = sum(small)
+            n_split = 1
+            if n_small:
+                longest = max(c for c, s in zip(step.ctx_lens, small) if s)
+                n_split = context_splits(n_small, longest, self.n_kv_heads, f["split_slots"])
+            plan = AttentionPlan(
+                n_tiles=sum(-(-r // f["tile_rows"]) for r in big),
+                n_tiles_tc=sum(-(-r // f["tc_rows"]) for r in big),
+                any_small=n_small > 0, n_split=n_split)
+            step.attn_tiles[key] = plan
+        return plan
+
+    def decode_graph_key(self, step: StepContext) -> tuple:
+        """What, besides the number of requests, fixes this mixer's launches in a step
+        of single tokens: the number of context splits."""
+        plan = self.plan(step)
+        if plan is None:
+            return ()
+        return ("gqa", self.n_kv_heads, self.n_heads // self.n_kv_heads, self.head_dim,
+                plan.n_split)
 
     def forward(self, h, step: StepContext, cache: CacheHandle):
         rt = self.runtime
@@ -68,6 +147,6 @@ class GroupedQueryAttention(Mixer):
                                            self.n_kv_heads)
         o = rt.buffer("attn_out", (t, self.n_heads * hd), rt.act_dtype)
         rt.ops.paged_attention(qkv, o, cache, step, self.n_heads, self.n_kv_heads,
-                               hd, self.scale, self.window or 0)
+                               hd, self.scale, self.window or 0, plan=self.plan(step))
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
         return rt.ops.linear_parts(o, self.wo, delta)

@@ -159,13 +159,27 @@ class ResidualStream:
 
 
 class Part:
-    """Base of every part; sizes and constants are constructor arguments."""
+    """Base of every part; sizes and constants are constructor arguments.
+
+    Capture into a CUDA graph is a part's own business.  The step function replays a
+    step of single decoded tokens from a graph only if every part of the model says
+    ``decode_capturable`` (its ``forward`` then only launches work on the current
+    stream: no wait for the device, no read of device memory by the host, no launch
+    that depends on values computed on the device) and keys the graph by the number of
+    requests plus what each part's ``decode_graph_key(step)`` adds (whatever else, known
+    on the host, changes its launches).  A part that says nothing is never captured.
+    """
+
+    decode_capturable = False
 
     def tensor_specs(self) -> dict:
         return {}
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
+
+    def decode_graph_key(self, step: "StepContext") -> tuple:
+        return ()
 
 
 class Norm(Part):

@@ -38,6 +38,13 @@ class PreNormBlock(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    @property
+    def decode_capturable(self) -> bool:
+        return all(getattr(p, "decode_capturable", False) for _, p in self._named_parts())
+
+    def decode_graph_key(self, step: StepContext) -> tuple:
+        return tuple(k for _, p in self._named_parts() if (k := p.decode_graph_key(step)))
+
     def forward(self, stream: ResidualStream, step: StepContext,
                 cache: CacheHandle) -> None:
         h = self.mixer_norm.forward(stream)

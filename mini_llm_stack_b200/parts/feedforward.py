@@ -14,6 +14,8 @@ from .base import FeedForward, StepContext, TensorSpec
 
 
 class SwiGLUFeedForward(FeedForward):
+    decode_capturable = True      # forward only launches kernels on the current stream
+
     def __init__(self, d_model: int, intermediate_size: int):
         self.d_model, self.intermediate_size = int(d_model), int(intermediate_size)
         self.w_gate_up = self.w_down = None

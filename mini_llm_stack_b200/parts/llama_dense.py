@@ -72,4 +72,5 @@ def build_llama_dense(cfg: DenseLlamaConfig) -> ComposedModel:
                          RMSNorm(cfg.d_model, cfg.norm_eps), head, aliases=folder_names)
 
 
-register_architecture("llama_dense", DenseLlamaConfig, build_llama_dense)
+register_architecture("llama_dense", DenseLlamaConfig, build_llama_dense,
+                      aliases=("LlamaForCausalLM",))

@@ -25,6 +25,8 @@ class LayerCall:
 class TokenEmbedding(Part):
     """``x[t] = E[token[t]]``; no scaling, no position term (train/model.py:239)."""
 
+    decode_capturable = True
+
     def __init__(self, vocab_size: int, d_model: int):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
         self.weight = None
@@ -45,6 +47,8 @@ class TokenEmbedding(Part):
 
 class OutputHead(Part):
     """``logits = h @ W^T`` in float32; W is the embedding table when tied."""
+
+    decode_capturable = True
 
     def __init__(self, vocab_size: int, d_model: int, tied_to: Optional[TokenEmbedding]):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
@@ -135,6 +139,25 @@ class ComposedModel:
     # -------------------------------------------------------------------- cache
     def cache_specs(self) -> list:
         return list(self._slot_specs)
+
+    # ------------------------------------------------------------------- graphs
+    def _all_parts(self) -> list:
+        return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    @property
+    def decode_capturable(self) -> bool:
+        """Whether a step of single decoded tokens may be replayed from a CUDA graph:
+        only if every part says so (``Part.decode_capturable``)."""
+        return all(getattr(p, "decode_capturable", False) for p in self._all_parts())
+
+    def decode_graph_key(self, step: StepContext) -> tuple:
+        """What the parts add to the key of a decode step's graph, without repeats."""
+        seen = []
+        for p in self._all_parts():
+            k = p.decode_graph_key(step)
+            if k and k not in seen:
+                seen.append(k)
+        return tuple(seen)
 
     # ------------------------------------------------------------------ forward
     def forward(self, step: StepContext, handles: list):

@@ -37,6 +37,9 @@ class Sampler:
         self.runtime = runtime
         self._cap = 0
         self._copied = torch.cuda.Event()        # the tokens of the last launch are on the host
+        # the kernels' status word travels with the tokens: a kernel that refused its
+        # input or gave up a wait is known in the step that ran it
+        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
         self._grow(max_rows)
 
     def _grow(self, n: int) -> None:
@@ -66,6 +69,7 @@ class Sampler:
         else:
             ops.sample(logits, None, None, self._out)
         self._out_host[:n].copy_(self._out[:n], non_blocking=True)
+        self._status_host.copy_(ops.status, non_blocking=True)
         self._copied.record(torch.cuda.current_stream(self.runtime.device))
         return n
 
@@ -75,6 +79,10 @@ class Sampler:
         return self._out[:n]
 
     def finish(self, n: int) -> list:
-        """Wait for the tokens of the last ``launch`` (not for work queued after it)."""
+        """Wait for the tokens of the last ``launch`` (not for work queued after it).
+        Raises ``KernelError`` if a kernel up to that launch set the status word."""
         self._copied.synchronize()
+        code = int(self._status_host[0])
+        if code:
+            self.runtime.ops.raise_for_status(code)
         return self._out_host[:n].tolist()

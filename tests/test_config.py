@@ -115,3 +115,56 @@ def test_registry_takes_another_architecture():
 def test_direct_construction_fills_the_arrangement():
     cfg = DenseLlamaConfig(n_layers=3, d_model=64, n_heads=4, n_kv_heads=2, head_dim=16)
     assert cfg.layer_order == (0, 1, 2) and cfg.layer_windows == (None, None, None)
+
+
+LLAMA_FOLDER_CONFIG = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "attention_bias": False,
+    "attention_dropout": 0.0, "bos_token_id": 128000, "eos_token_id": 128001,
+    "hidden_act": "silu", "hidden_size": 2048, "initializer_range": 0.02,
+    "intermediate_size": 8192, "max_position_embeddings": 8192, "mlp_bias": False,
+    "num_attention_heads": 32, "num_hidden_layers": 16, "num_key_value_heads": 8,
+    "pretraining_tp": 1, "rms_norm_eps": 1e-05, "rope_scaling": None, "rope_theta": 500000.0,
+    "tie_word_embeddings": True, "torch_dtype": "bfloat16", "transformers_version": "4.45.0",
+    "use_cache": True, "vocab_size": 128256, "head_dim": 64,
+}
+
+
+def test_a_llama_model_folders_config_is_read():
+    """The spellings and the extra keys usual in Llama model folders: aliases are
+    mapped, keys without meaning for the math are dropped, the architecture name is
+    an alias of ``llama_dense``."""
+    cfg = config_from_dict(LLAMA_FOLDER_CONFIG)
+    assert isinstance(cfg, DenseLlamaConfig) and cfg.architecture == "llama_dense"
+    assert (cfg.d_model, cfg.n_layers, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim) == \
+        (2048, 16, 32, 8, 64)
+    assert cfg.intermediate_size == 8192 and cfg.vocab_size == 128256
+    assert cfg.tie_embeddings and cfg.dtype == "bfloat16" and cfg.norm_eps == 1e-5
+    assert lookup_architecture("LlamaForCausalLM") is lookup_architecture("llama_dense")
+    assert build_model(cfg).tied_names() == {"lm_head.weight": "embed.weight"}
+
+
+@pytest.mark.parametrize("key,value", [
+    ("rope_scaling", {"rope_type": "llama3", "factor": 8.0}), ("attention_bias", True),
+    ("mlp_bias", True), ("hidden_act", "gelu"), ("sliding_window", 4096),
+    ("attention_dropout", 0.1)])
+def test_keys_that_change_the_math_are_refused_by_name(key, value):
+    with pytest.raises(ConfigError, match=key):
+        config_from_dict(dict(LLAMA_FOLDER_CONFIG, **{key: value}))
+
+
+def test_an_unknown_key_is_still_an_error():
+    with pytest.raises(ConfigError, match="some_new_switch"):
+        config_from_dict(dict(LLAMA_FOLDER_CONFIG, some_new_switch=1))
+
+
+def test_engine_options_refuse_what_contradicts_the_loaded_model():
+    from mini_llm_stack_b200.config import EngineOptions
+    opts = EngineOptions(dtype="bf16", kv_dtype="bfloat16", device="cpu", seed=5)
+    assert opts.dtype == "bfloat16" and opts.seed == 5
+    opts.check_against("bfloat16", "cpu")
+    with pytest.raises(ConfigError, match="kv_dtype"):
+        EngineOptions(kv_dtype="float32", device="cpu").check_against("bfloat16", "cpu")
+    with pytest.raises(ConfigError, match="dtype"):
+        EngineOptions(dtype="float32", device="cpu").check_against("bfloat16", "cpu")
+    with pytest.raises(ConfigError, match="device"):
+        EngineOptions(device="cuda:1").check_against("bfloat16", "cuda:0")

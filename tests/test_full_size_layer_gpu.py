@@ -4,7 +4,10 @@ The tiny configurations never reach the paths that large sizes take: several
 waves of GEMM tiles, split-K in the weight-major orientation, the tcgen05
 attention kernel with head 128 and four query heads a kv head, context splits in
 decode attention.  One layer with a small vocabulary keeps the plain
-implementation on the CPU affordable.
+implementation on the CPU affordable.  Two more tests run the plain implementation
+on the GPU (true float32 products, no reduced-precision matrix mode): one layer in
+float32 at the full layer sizes, and four layers in bfloat16 with a request whose
+context ends above 8,000 tokens.
 """
 
 import pytest
@@ -17,6 +20,7 @@ from safetensors.torch import load_file
 from tiny_configs import plain_cfg
 
 pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
 
 BIG = dict(architecture="llama_dense", vocab_size=1000, d_model=4096, n_layers=1, n_heads=32,
            n_kv_heads=8, head_dim=128, intermediate_size=14336, max_seq_len=1024,
@@ -86,3 +90,132 @@ def test_chained_launches_do_not_change_a_bit(big):
         chained = run(True)
         for r in "abc":
             assert torch.equal(chained[r], plain[r]), f"request {r} differs under chained launches"
+
+
+# --------------------------------------------------------------------------------------
+# the plain implementation on the GPU, weights drawn on the device
+# --------------------------------------------------------------------------------------
+def device_model(raw, dtype, seed, wq_scale=1.0):
+    """(bound model, plain config, float32 weights on the device by name): random
+    weights drawn on the device, N(0, 0.02), norm weights 1 + N(0, 0.1); ``wq_scale``
+    multiplies every query projection, which sharpens the attention so that single
+    far keys carry weight (a wrong page then shows in the logits)."""
+    from mini_llm_stack_b200.config.registry import build_model
+    from mini_llm_stack_b200.ops.kernels import Runtime
+    cfg = config_from_dict(dict(raw, dtype=dtype))
+    tdtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    model = build_model(cfg)
+    gen = torch.Generator(device=DEV).manual_seed(seed)
+    tensors = {}
+    for name, spec in model.tensor_specs().items():
+        t = torch.empty(spec.shape, dtype=torch.float32, device=DEV)
+        if spec.init == "normal":
+            t.normal_(0.0, 0.02, generator=gen)
+            if name.endswith("wq.weight"):
+                t *= wq_scale
+        else:
+            t.normal_(1.0, 0.1, generator=gen)
+        tensors[name] = t.to(tdtype)
+    w = {n: t.float() for n, t in tensors.items()}
+    model.bind(tensors, Runtime(DEV, tdtype))
+    return model, plain_cfg(raw), w
+
+
+@pytest.fixture
+def true_float32_products():
+    """The plain implementation's products on the GPU in full float32."""
+    old = (torch.backends.cuda.matmul.allow_tf32, torch.get_float32_matmul_precision())
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.set_float32_matmul_precision("highest")
+    yield
+    torch.backends.cuda.matmul.allow_tf32 = old[0]
+    torch.set_float32_matmul_precision(old[1])
+
+
+def replay_on(model, num_blocks, max_requests=4):
+    from engine_helpers import Replayer
+    from mini_llm_stack_b200.engine.runner import ModelRunner
+    rp = Replayer.__new__(Replayer)
+    rp.model = model
+    rp.runner = ModelRunner(model, num_blocks=num_blocks, block_size=16,
+                            max_requests=max_requests)
+    rp.fed, rp.rows = {}, {}
+    return rp
+
+
+def test_float32_at_full_layer_sizes(true_float32_products):
+    """The true 32-bit path at hidden 4096, feed-forward 14336 and 32 / 8 heads of 128:
+    a prompt in portions, a second request beside it, decoded tokens."""
+    model, cfg, w = device_model(BIG, "float32", seed=6)
+    toks = {"a": tokens_for(1000, 300, 11), "b": tokens_for(1000, 45, 12)}
+    rp = replay_on(model, num_blocks=32)
+    rp.step([("a", 150)], toks)
+    rp.step([("a", 120), ("b", 40)], toks)
+    for _ in range(5):
+        rp.step([("a", 1), ("b", 1)], toks)
+    rp.step([("a", 25)], toks, end=["a", "b"])
+    for r in "ab":
+        want = plain_logits(w, cfg, toks[r], "float32").cpu()
+        assert_close(rp.logits(r), want, "float32", f"float32 full-size layer, request {r}")
+
+
+DEEP = dict(BIG, n_layers=4, max_seq_len=8192)
+
+
+def test_bfloat16_four_layers_with_a_context_above_8000(true_float32_products):
+    """Four layers at the full layer sizes, one request of 8,150 tokens: the prompt in
+    two steps, the last 32 tokens one by one (context splits over 8,000 cached keys,
+    merged), a short request beside it.  The query projections are scaled up so that
+    attention rests on fewer keys anywhere in the context.
+
+    The bound is measured, not chosen.  The engine cannot round exactly where the plain
+    implementation does (its probabilities are rounded relative to a running maximum,
+    its gate and up projections are never stored), and at this width and depth those
+    independent roundings add up to more than the tiny models' tolerance, in the
+    tensor-core kernels and in the CUDA-core attention kernel alike.  So the yardstick
+    is what bfloat16 storage itself does to the plain implementation: the engine must be
+    no further from the plain run with bfloat16 roundings than that run is from the plain
+    run without any.  A wrong page, mask or split is off by the logits' own size."""
+    model, cfg, w = device_model(DEEP, "bfloat16", seed=8, wq_scale=2.0)
+    n = 8150
+    toks = {"long": tokens_for(1000, n, 21), "short": tokens_for(1000, 40, 22)}
+    rp = replay_on(model, num_blocks=n // 16 + 8)
+
+    def step(portions, end=()):
+        # only the last rows are wanted of the long prompt's portions: keeping 8,000
+        # rows of logits on the host serves nothing
+        from mini_llm_stack_b200.engine.batch import Entry
+        entries = []
+        for rid, cnt in portions:
+            b = rp.fed.get(rid, 0)
+            want = list(range(cnt)) if cnt <= 64 else list(range(cnt - 8, cnt))
+            entries.append((rid, cnt, Entry(rid, toks[rid][b:b + cnt], want)))
+        rp.runner.reserve([e for _, _, e in entries])
+        logits = rp.runner.step([e for _, _, e in entries]).float().cpu()
+        at = 0
+        for rid, cnt, e in entries:
+            b = rp.fed.get(rid, 0)
+            for j, wnt in enumerate(e.want):
+                rp.rows.setdefault(rid, {})[b + wnt] = logits[at + j]
+            at += len(e.want)
+            rp.fed[rid] = b + cnt
+        for rid in end:
+            rp.runner.release(rid)
+        rp.model.runtime.ops.check_status()
+
+    step([("long", 4096)])
+    step([("long", n - 32 - 4096), ("short", 8)])
+    for i in range(32):
+        step([("long", 1), ("short", 1)])
+    for rid in ("long", "short"):
+        rows = sorted(rp.rows[rid])
+        got = torch.stack([rp.rows[rid][r] for r in rows])
+        rounded = plain_logits(w, cfg, toks[rid], "bfloat16").cpu()[rows]
+        exact = plain_logits(w, cfg, toks[rid], "float32").cpu()[rows]
+        storage_noise = (rounded - exact).abs().max().item()
+        err = (got - rounded).abs().max().item()
+        print(f"request {rid}: engine - plain {err:.4f}, bfloat16 storage noise of the plain "
+              f"{storage_noise:.4f}, largest logit {rounded.abs().max().item():.3f}")
+        assert storage_noise < 0.05 * rounded.abs().max().item()      # the yardstick is small
+        assert err <= storage_noise, f"four layers, request {rid}: {err} > {storage_noise}"
+    assert max(rp.rows["long"]) == n - 1 and len(rp.rows["long"]) == 8 + 8 + 32

@@ -17,7 +17,21 @@ ROOT = Path(__file__).resolve().parent.parent
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     tmp = tmp_path_factory.mktemp("gen_models")
-    return {(k, d): make_folder(tmp, k, d) for k in "ABC" for d in ("float32", "bfloat16")}
+    out = {(k, d): make_folder(tmp, k, d) for k in "ABC" for d in ("float32", "bfloat16")}
+    # heads of 64 and 128: bfloat16 runs go through the tcgen05 / TMA attention kernels,
+    # the fused gate-up product and the weight-major products of large models
+    out.update({(k, "bfloat16"): make_folder(tmp, k, "bfloat16") for k in "DE"})
+    return out
+
+
+def assert_tokens_are_maxima(w, cfg, prompt, generated, what=""):
+    """Every generated token is, within the bfloat16 comparisons' tolerance, a largest
+    logit of the plain implementation run on the sequence the engine itself produced
+    (two runs may part at a near tie, so the tokens are not compared with each other)."""
+    logits = P.plain_forward(w, cfg, list(prompt) + list(generated), RND["bfloat16"])
+    for i, tok in enumerate(generated):
+        row = logits[len(prompt) - 1 + i]
+        assert row[tok] >= row.max() - 1e-2 * row.abs().max(), (what, i, tok)
 
 
 def test_greedy_generation_matches_plain_token_for_token(folders):
@@ -189,3 +203,89 @@ def test_many_requests_arriving_ending_and_giving_way_with_steps_launched_ahead(
         if j["eos"] is not None and j["eos"] in want:
             want = want[:want.index(j["eos"]) + 1]
         assert ahead[i] == want
+
+
+# --------------------------------------------------------------------------------------
+# bfloat16 through the scheduler, on the kernels large models use (heads of 64 and 128)
+# --------------------------------------------------------------------------------------
+@pytest.mark.parametrize("key", ["D", "E"])
+def test_bfloat16_running_out_of_pages(folders, key):
+    """Requests give way and are recomputed: the recomputation goes through the prompt
+    kernels where the first run decoded, so the bits differ within rounding and every
+    token is still a maximum of the plain logits."""
+    folder, cfg, w = folders[(key, "bfloat16")]
+    vocab = cfg["vocab_size"]
+    prompts = [tokens_for(vocab, n, 50 + n) for n in (70, 131, 7, 44, 150, 26)]
+    tight = LLM.from_folder(folder, dtype="bfloat16", num_blocks=30, max_batch=6, chunk_size=96,
+                            max_tokens_per_step=128)
+    got = tight.generate(prompts, max_new_tokens=40)
+    assert tight.engine.scheduler.preemptions > 0
+    tight.engine.cache.check()
+    assert tight.engine.cache.num_free_pages() == 30
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        assert len(g) == 40
+        assert_tokens_are_maxima(w, cfg, p, g, f"tiny-{key} request {i}")
+
+
+@pytest.mark.parametrize("key", ["D", "E"])
+def test_bfloat16_steps_launched_ahead(folders, key):
+    """Launching the next decode step before this one's tokens are on the host: end
+    tokens known a step late, an end by count, a late arrival; bfloat16, CUDA graphs."""
+    folder, cfg, w = folders[(key, "bfloat16")]
+    vocab = cfg["vocab_size"]
+    prompts = [tokens_for(vocab, n, 70 + n) for n in (3, 140, 29, 65)]
+    news = {0: 40, 1: 23, 2: 40, 3: 30}
+
+    def run(launch_ahead, eos):
+        llm = LLM.from_folder(folder, dtype="bfloat16", num_blocks=64, max_batch=4,
+                              launch_ahead=launch_ahead)
+        eng = llm.engine
+        reqs = [eng.submit(prompts[i], news[i], eos.get(i)) for i in range(3)]
+        late = None
+        while eng.step():
+            if late is None and eng.steps == 6:
+                late = eng.submit(prompts[3], news[3], None)
+        assert late is not None and not eng.step()
+        eng.cache.check()
+        return [list(r.generated) for r in reqs + [late]], eng
+
+    free, _ = run(False, {})
+    eos = {0: free[0][5], 2: free[2][17]}          # end tokens that do occur
+    ahead, eng = run(True, eos)
+    assert any(k != "moved" and isinstance(v, tuple) for k, v in eng.runner._graphs.items())
+    for i, g in enumerate(ahead):
+        assert_tokens_are_maxima(w, cfg, prompts[i], g, f"tiny-{key} request {i}")
+        if i in eos:
+            assert g[-1] == eos[i] or len(g) == news[i]
+            assert eos[i] not in g[:-1]
+        else:
+            assert len(g) == news[i]
+
+
+def test_bfloat16_chunked_prompts_with_pages_of_eight(folders):
+    folder, cfg, w = folders[("D", "bfloat16")]
+    prompts = [tokens_for(cfg["vocab_size"], n, 30 + n) for n in (1, 9, 140, 77)]
+    llm = LLM.from_folder(folder, dtype="bfloat16", num_blocks=96, block_size=8, max_batch=4,
+                          chunk_size=48, max_tokens_per_step=80)
+    got = llm.generate(prompts, max_new_tokens=20, temperature=0.0)
+    assert max(llm.engine.step_tokens) <= 80
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        assert_tokens_are_maxima(w, cfg, p, g, f"request {i}")
+
+
+def test_a_kernels_refusal_raises_in_the_step_that_ran_it(folders):
+    """The status word comes back with the sampled tokens.  The failure is made on the
+    host: a token id outside the vocabulary slips past the batch builder (its check is
+    switched off here); the embedding kernel answers with zeros and a status bit, and
+    the step that ran it raises.  Nothing faults on the device."""
+    from mini_llm_stack_b200.ops.kernels import KernelError
+    folder, cfg, w = folders[("A", "float32")]
+    llm = LLM.from_folder(folder, dtype="float32", num_blocks=32)
+    eng = llm.engine
+    eng.submit([5, 17, 3], max_new_tokens=3)
+    eng.run_until_done()
+    eng.runner.builder.vocab_size = 1 << 30
+    eng.submit([5, 400, 7], max_new_tokens=4)            # 400 is not among 256 tokens
+    with pytest.raises(KernelError, match="token id outside the vocabulary"):
+        eng.step()
+    eng.model.runtime.ops.check_status()                 # the word was cleared

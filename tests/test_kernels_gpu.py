@@ -9,6 +9,7 @@ import plain_llama as P
 from mini_llm_stack_b200.cache.manager import CacheManager
 from mini_llm_stack_b200.engine.batch import BatchBuilder, Entry
 from mini_llm_stack_b200.ops.kernels import KernelError, Runtime
+from mini_llm_stack_b200.parts.attention import GroupedQueryAttention
 from mini_llm_stack_b200.parts.base import PagedKV
 
 pytestmark = pytest.mark.gpu
@@ -259,6 +260,24 @@ def test_argmax_and_temperature_sampling(rts, vocab):
 
 
 # ------------------------------------------------------------------ rope and store
+def owned_slots(block, pages, lens, starts, seed):
+    """Slots as the cache hands them out: request r brings ``lens[r]`` tokens, the first
+    at offset ``starts[r]`` of a page of its own; its tokens take consecutive slots and
+    go on into further pages of its own.  Returns (int32 slots, set of (page, offset)
+    the kernel must clear: the rest of the page a request's last token lies in, if that
+    page was entered in this step)."""
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    slots, cleared = [], set()
+    for n, s in zip(lens, starts):
+        assert 0 <= s < block
+        mine = [order.pop() for _ in range((s + n + block - 1) // block)]
+        slots += [mine[(s + i) // block] * block + (s + i) % block for i in range(n)]
+        last = s + n - 1
+        if last // block > 0 or s == 0:
+            cleared |= {(mine[last // block], o) for o in range(last % block + 1, block)}
+    return torch.tensor(slots, dtype=torch.int32), cleared
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads, kv, hd, theta, block", [(4, 2, 16, 10000.0, 4), (3, 1, 32, 5e5, 8),
                                                          (5, 5, 48, 25000.0, 16), (8, 2, 128, 5e5, 16)])
@@ -268,7 +287,9 @@ def test_rope_store(rts, dtype, heads, kv, hd, theta, block):
     cos, sin = P.plain_rotary_tables(hd, max_pos, theta)
     qkv = rand((t, (heads + 2 * kv) * hd), dtype, 16)
     pos = torch.randint(0, max_pos, (t,), generator=torch.Generator().manual_seed(17)).int()
-    slots = torch.randperm(pages * block, generator=torch.Generator().manual_seed(18))[:t].int()
+    # three requests: a single token entering a page, a portion that starts and ends
+    # inside pages it already had or enters, a portion that ends at a page's last slot
+    slots, cleared = owned_slots(block, pages, [1, 9, 13], [0, block - 3, (-13) % block], 18)
     k_pool = torch.full((kv, pages, block, hd), 7.0, dtype=dtype, device=DEV)
     v_pool = torch.full((kv, pages, block, hd), 7.0, dtype=dtype, device=DEV)
     src = qkv.float().cpu()
@@ -289,7 +310,15 @@ def test_rope_store(rts, dtype, heads, kv, hd, theta, block):
         pg, off = int(slots[i]) // block, int(slots[i]) % block
         assert torch.equal(kp[:, pg, off], want_k[i]) and torch.equal(vp[:, pg, off], v[i])
         touched[pg, off] = True
-    untouched = ~touched[None, :, :].expand(kv, pages, block)
+    # the rest of a page entered in this step is cleared (what its previous owner left
+    # must not reach a tensor-core kernel as 0 * NaN); everything else is untouched
+    zeroed = torch.zeros(pages, block, dtype=torch.bool)
+    for pg, off in cleared:
+        zeroed[pg, off] = True
+    assert cleared and not bool((zeroed & touched).any())
+    z = zeroed[None, :, :].expand(kv, pages, block)
+    assert bool((kp[z] == 0.0).all()) and bool((vp[z] == 0.0).all())
+    untouched = ~(touched | zeroed)[None, :, :].expand(kv, pages, block)
     assert bool((kp[untouched] == 7.0).all()) and bool((vp[untouched] == 7.0).all())
     # a call that reads another call's cache rotates its queries and writes nothing
     k2 = k_pool.clone()
@@ -311,7 +340,7 @@ def test_rope_store_of_many_tokens_gives_the_bits_of_few_tokens(rts, heads, kv, 
     cos, sin = (x.to(DEV) for x in P.plain_rotary_tables(hd, max_pos, 5e5))
     qkv = rand((t, width), torch.bfloat16, 51)
     pos = torch.randint(0, max_pos, (t,), generator=torch.Generator().manual_seed(52)).int().to(DEV)
-    slots = torch.randperm(pages * block, generator=torch.Generator().manual_seed(53))[:t].int().to(DEV)
+    slots = owned_slots(block, pages, [t], [0], 53)[0].to(DEV)     # one request's next t tokens
     pools = [torch.full((kv, pages, block, hd), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
     many = qkv.clone()
     ops.rope_store(many, pos, cos, sin, slots, pools[0], pools[1], t, heads, kv, hd, max_pos, True)
@@ -346,7 +375,7 @@ def test_rope_store_reads_rows_from_the_parts_of_a_product(rts, heads, kv, hd, b
         summed += parts[k]
     qkv = summed.to(torch.bfloat16)
     pos = torch.randint(0, max_pos, (t,), generator=torch.Generator().manual_seed(32)).int().to(DEV)
-    slots = torch.randperm(pages * block, generator=torch.Generator().manual_seed(33))[:t].int().to(DEV)
+    slots = owned_slots(block, pages, [4, 5], [0, block - 2], 33)[0].to(DEV)
     pools = [torch.full((kv, pages, block, hd), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
     ops.rope_store(qkv, pos, cos, sin, slots, pools[0], pools[1], t, heads, kv, hd, max_pos, True)
     got = torch.full((t, width), 3.0, dtype=torch.bfloat16, device=DEV)
@@ -406,9 +435,13 @@ class AttnCase:
             qkv[at:at + n, :self.heads * self.hd] = q.transpose(0, 1).reshape(n, -1)
             at += n
         out = torch.empty((t, self.heads * self.hd), dtype=rt.act_dtype, device=DEV)
+        # the part plans the launches (tiles, small requests, context splits)
+        mixer = GroupedQueryAttention(self.heads * self.hd, self.heads, self.kv, self.hd,
+                                      self.hd ** -0.5, position=None, window=self.window)
         rt.ops.require_attention(self.hd)
+        mixer._facts = rt.ops.attention_facts(self.hd)
         rt.ops.paged_attention(qkv, out, self.handle, step, self.heads, self.kv, self.hd,
-                               self.hd ** -0.5, self.window or 0)
+                               self.hd ** -0.5, self.window or 0, plan=mixer.plan(step))
         torch.cuda.synchronize()
         return out.float().cpu()
 
@@ -538,6 +571,29 @@ def test_window_edge(rts, dtype, window, ctx, q_len):
     assert bool(((got - want).abs().max(dim=1).values <= attn_tol(dtype, ctx) * row_scale).all())
 
 
+@pytest.mark.parametrize("heads, kv, hd", [(4, 2, 64), (8, 2, 128)])
+@pytest.mark.parametrize("window, ctx, q_len", [(150, 1000, 1), (77, 700, 2), (150, 900, 130),
+                                                (200, 1300, 300), (77, 520, 300), (33, 400, 1)])
+def test_window_edge_with_heads_of_64_and_128(rts, heads, kv, hd, window, ctx, q_len):
+    """The same on the kernels bfloat16 takes for these head sizes: tcgen05 tiles whose
+    first key tile starts at a window's edge, the TMA split kernel, and their zero-fill
+    of pages the window has given back (the contexts are long enough for that).  The
+    windows are no multiples of a tile of keys."""
+    rt = rts[torch.bfloat16]
+    case = AttnCase(rt, heads, kv, hd, 16, [ctx], [q_len], window=window, seed=6)
+    q, k, v = case.q[0], case.k[0], case.v[0]
+    outside = ctx - 1 - window                     # hidden from the last query
+    k[:, outside] = q[0, -1] * 3
+    v[:, outside] = 1000.0
+    got, want = case.run(), case.want()
+    rt.ops.check_status()
+    assert -1 in case.cache.pages_of(0)            # pages were given back before the portion
+    assert got[-1].abs().max().item() < 100
+    row_scale = want.abs().max(dim=1).values.clamp(min=1.0)
+    assert bool(((got - want).abs().max(dim=1).values
+                 <= attn_tol(torch.bfloat16, ctx) * row_scale).all())
+
+
 def test_attention_refuses_head_sizes_it_does_not_have(rts):
     with pytest.raises(KernelError, match="steps of 16"):
         rts[torch.bfloat16].ops.require_attention(40)
@@ -545,18 +601,20 @@ def test_attention_refuses_head_sizes_it_does_not_have(rts):
         rts[torch.float32].ops.require_attention(272)
 
 
-@pytest.mark.parametrize("block", [8, 16, 32, 64])
-def test_bf16_attention_kernels_agree_with_each_other(rts, block):
+@pytest.mark.parametrize("block, window", [(8, None), (16, None), (32, None), (64, None),
+                                           (16, 150), (32, 333)])
+def test_bf16_attention_kernels_agree_with_each_other(rts, block, window):
     """tcgen05 tiles + TMA split kernel ("auto"), mma.sync kernels with TMA loads
     ("mma"), the same with plain asynchronous copies ("no_tma") and the CUDA-core
-    kernel ("simt"), on the same pages."""
+    kernel ("simt"), on the same pages; also with a window that has given pages back."""
     rt = rts[torch.bfloat16]
     ctxs, q_lens = [500, 77, 1200, 300, 2100], [1, 77, 2, 150, 1]
     got = {}
     try:
         for impl in ("auto", "mma", "no_tma", "simt"):
             rt.ops.attention_impl = impl
-            got[impl] = AttnCase(rt, 8, 2, 128, block, ctxs, q_lens, seed=21).run()
+            got[impl] = AttnCase(rt, 8, 2, 128, block, ctxs, q_lens, window=window,
+                                 seed=21).run()
     finally:
         rt.ops.attention_impl = "auto"
     rt.ops.check_status()

@@ -142,6 +142,43 @@ def test_attention_part_portion_after_cached_context(rts, dtype, heads, kv, hd, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv, hd, d, window", [(4, 2, 64, 128, None), (8, 2, 128, 256, None),
+                                                      (8, 2, 128, 256, 150), (4, 2, 32, 64, None)])
+def test_what_a_page_held_before_does_not_reach_its_next_owner(rts, dtype, heads, kv, hd, d, window):
+    """The whole pool is NaN, as a request that overflowed might have left its pages.
+    A new request's keys and values go in through the mixer's position part, which
+    clears the rest of every page it enters; the tensor-core kernels mask scores, not
+    values, so a leftover NaN in a slot past the context would come out as 0 * NaN.
+    Prompts of several tiles, portions of two tokens, decoded tokens; with a window,
+    pages it has given back are read as zeros."""
+    rt = rts[dtype]
+    pos = RotaryPosition(hd, 10000.0, 1024)
+    mixer = GroupedQueryAttention(d, heads, kv, hd, hd ** -0.5, pos, window=window)
+    w = draw(mixer, dtype, 15)
+    mixer.bind(w, rt)
+    cache = CacheManager([mixer.cache_spec()], 48, 16, 2, 1024, device=DEV, kv_dtype=dtype)
+    cache.paged[0].kv.fill_(float("nan"))
+    handle = cache.handles()[0]
+    portions = (131, 2, 1, 300, 1, 1, 2, 67, 1)
+    n = sum(portions)
+    h_all = (torch.randn(n, d, device=DEV) * 0.5).to(dtype)
+    outs, at = [], 0
+    for portion in portions:
+        step = step_for(cache, [("r", [0] * portion)])
+        outs.append(mixer.forward(h_all[at:at + portion].contiguous(), step, handle).float().clone())
+        cache.commit("r", portion)
+        at += portion
+    got = torch.cat(outs)
+    assert bool(torch.isfinite(got).all())
+    cfg = dict(n_heads=heads, n_kv_heads=kv, head_dim=hd)
+    cos, sin = P.plain_rotary_tables(hd, 1024, 10000.0)
+    f = {f"m.{k}": v.float().cpu() for k, v in w.items()}
+    want, _ = P.plain_mixer(h_all.float().cpu(), f, "m", cfg, cos, sin, torch.arange(n), window,
+                            rnd_of(dtype))
+    assert close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_block_part_wires_norms_mixer_and_feed_forward(rts, dtype):
     rt = rts[dtype]
     d, heads, kv, hd, inter, eps = 96, 3, 1, 32, 256, 1e-6

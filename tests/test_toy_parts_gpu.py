@@ -51,10 +51,20 @@ class ToyConfig:
 
 
 class DecayMixer(Mixer):
-    """``s_t = decay * s_{t-1} + h_t``; ``out_t = W s_t``.  State: s, per request."""
+    """``s_t = decay * s_{t-1} + h_t``; ``out_t = W s_t``.  State: s, per request.
+
+    A step of single tokens runs on the device alone (indexed reads and writes of the
+    state, one product), so the mixer agrees to be captured into the decode graph and
+    adds its own word to the graph's key; portions of prompts walk their tokens on the
+    host, which is never captured."""
+
+    decode_capturable = True
 
     def __init__(self, d_model, decay):
         self.d, self.decay = d_model, decay
+
+    def decode_graph_key(self, step):
+        return ("decay", self.d)
 
     def tensor_specs(self):
         return {"w.weight": TensorSpec((self.d, self.d))}
@@ -67,6 +77,11 @@ class DecayMixer(Mixer):
         self.w = tensors["w.weight"].float()
 
     def forward(self, h, step, cache):
+        if step.max_q_len == 1 and self.decode_capturable:
+            slots = step.state_slot.long()
+            s = self.decay * cache.state[slots] + h.float()
+            cache.state.index_copy_(0, slots, s)
+            return (s @ self.w.t()).to(h.dtype)
         out = torch.empty_like(h)
         slots = step.state_slot.tolist()
         at = 0
@@ -149,6 +164,71 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         assert cache.slots.num_free == 3
     finally:
         unregister_architecture("toy_decay")
+
+
+def plain_toy_generate(w, cfg, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(plain_toy(w, cfg, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+class HostWalkingDecayMixer(DecayMixer):
+    """The same mixer without the device-only path: every step reads the slots on the
+    host, so it must never be captured, and says so."""
+
+    decode_capturable = False
+
+
+def build_toy_host_walking(cfg):
+    model = build_toy(cfg)
+    for blk in model.blocks:
+        if isinstance(blk.mixer, DecayMixer):
+            blk.mixer.__class__ = HostWalkingDecayMixer
+    return model
+
+
+@pytest.mark.parametrize("capturable", [True, False])
+def test_toy_mixer_through_the_scheduler_with_graphs_and_preemption(tmp_path, capturable):
+    """The toy architecture through ``LLM.generate``: so few pages that requests give
+    way and are recomputed (their state slots are given back, claimed again and start
+    from zero), many decode-only steps in a row, CUDA graphs on by default.  With the
+    capturable mixer those steps are replayed from a graph keyed also by the mixer's
+    own word; with a mixer that reads device memory on the host nothing is captured.
+    Either way the tokens are the plain implementation's."""
+    from mini_llm_stack_b200.engine.llm import LLM
+    name = "toy_decay" if capturable else "toy_decay_host"
+    register_architecture(name, ToyConfig, build_toy if capturable else build_toy_host_walking)
+    try:
+        cfg = ToyConfig(architecture=name)
+        write_random_model(tmp_path / "toy", cfg, seed=2, norm_std=0.1)
+        w = {n: t.float().clone() for n, t in
+             load_file(str(tmp_path / "toy" / "model.safetensors")).items()}
+        prompts = [tokens_for(cfg.vocab_size, n, 90 + n) for n in (20, 31, 7, 26)]
+        llm = LLM.from_folder(tmp_path / "toy", dtype="float32", num_blocks=7, max_batch=3,
+                              chunk_size=16, max_tokens_per_step=24)
+        assert llm.engine.runner.cuda_graphs and llm.model.decode_capturable == capturable
+        got = llm.generate(prompts, max_new_tokens=24)
+        eng = llm.engine
+        assert eng.scheduler.preemptions > 0
+        # at least three steps in a row in which every running request decoded one token
+        runs, best = 0, 0
+        for n in eng.step_tokens:
+            runs = runs + 1 if n <= 3 else 0
+            best = max(best, runs)
+        assert best >= 3
+        captured = [k for k, v in eng.runner._graphs.items()
+                    if k != "moved" and isinstance(v, tuple)]
+        if capturable:
+            assert captured and all(repr(("decay", cfg.d_model)) in repr(k[1]) for k in captured)
+        else:
+            assert not captured
+        for p, g in zip(prompts, got):
+            assert g == plain_toy_generate(w, cfg, p, 24)
+        eng.cache.check()
+        assert eng.cache.slots.num_free == 3 and eng.cache.num_free_pages() == 7
+    finally:
+        unregister_architecture(name)
 
 
 # ---------------------------------------------------------------------------------------
