@@ -498,8 +498,8 @@ class Ops:
             _need(temperature.dtype == torch.float32 and uniform.dtype == torch.float32,
                   "sample: temperature and uniform must be float32")
         scratch = None
-        if temperature is None and v > 4096:
-            scratch = self.scratch("argmax_chunks", 2 * n * ((v + 4095) // 4096))
+        if v > 4096:             # chunks of the vocabulary on many SMs, then a pick a row
+            scratch = self.scratch("argmax_chunks", 3 * n * ((v + 4095) // 4096))
         self.launches += 2 if scratch is not None else 1
         _check(self._sample(_ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), n, v,
                             _ptr(scratch), self._stream()), "sample")

@@ -259,6 +259,35 @@ def test_argmax_and_temperature_sampling(rts, vocab):
             assert abs(cum[min(got, want)].item() - us[i].item()) < 1e-5, (i, got, want)
 
 
+@pytest.mark.parametrize("vocab", [4097, 5000, 50000, 128256])
+def test_temperature_sampling_over_chunks_of_the_vocabulary(rts, vocab):
+    """Large vocabularies are sampled in chunks on many SMs; many rows, temperatures and
+    uniform numbers (0 and just below 1 among them) against the plain inverse CDF."""
+    ops = rts[torch.float32].ops
+    n = 48
+    g = torch.Generator().manual_seed(vocab)
+    logits = rand((n, vocab), torch.float32, 77, 3.0)
+    logits[5, vocab - 1] += 30.0                     # nearly all weight on the last token
+    logits[6, 0] += 30.0                             # ... on the first
+    logits[7, 4096] += 30.0                          # ... on a chunk's first token
+    temps = (torch.rand(n, generator=g) * 1.5 + 0.05).to(DEV)
+    temps[9] = 0.0                                   # a greedy row among them
+    us = torch.rand(n, generator=g).to(DEV)
+    us[0], us[1], us[2] = 0.0, 0.99999994, 0.5
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temps, us, out)
+    assert out[9].item() == int(torch.argmax(logits[9]))
+    assert out[5].item() == vocab - 1 or us[5].item() < 1e-6
+    for i in range(n):
+        want = P.plain_sample(logits[i].cpu(), temps[i].item(), us[i].item())
+        got = out[i].item()
+        if got != want:      # u may sit within rounding of a step of the cumulative sum
+            z = logits[i].cpu().double() / temps[i].item()
+            cum = torch.cumsum(torch.softmax(z, 0), 0)
+            assert abs(cum[min(got, want)].item() - us[i].item()) < 1e-5, (i, got, want)
+            assert abs(got - want) <= 64 or cum[max(got, want) - 1] - cum[min(got, want)] < 1e-5
+
+
 # ------------------------------------------------------------------ rope and store
 def owned_slots(block, pages, lens, starts, seed):
     """Slots as the cache hands them out: request r brings ``lens[r]`` tokens, the first
