@@ -326,6 +326,195 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same product with pairs of CTAs (tcgen05 cta_group::2) for prompts: a cluster of two
+// CTAs on neighbouring SMs owns a tile of 256 rows of A by 256 rows of B.  Each CTA brings
+// in its 128 rows of A and its half (128 rows) of the B tile, so an SM reads 32 KB of
+// shared memory a k-block where a lone CTA with the same 128 x 256 share of the output
+// reads 48 KB; the instruction, issued by one thread of the pair's first CTA, multiplies
+// both CTAs' A rows with both halves of B and leaves each CTA its 128 rows of the result
+// in its own tensor memory.
+//
+// Hand-overs inside the pair:
+//   full[s]       this CTA's TMA copies of stage s have landed (own barrier, byte count);
+//   peer_full[s]  (first CTA) the second CTA's copies of stage s have landed: its warp 1
+//                 waits on its own full[s] and arrives here across the cluster;
+//   empty[s]      the instructions reading stage s are done: tcgen05.commit arrives on
+//                 both CTAs' barriers at once;
+//   acc_full[a]   accumulator a is complete: commit to both CTAs;
+//   acc_empty[a]  (first CTA) both CTAs' epilogue warps have read accumulator a: four local
+//                 arrivals and four from the second CTA.
+// All loads are plain TMA loads into the CTA's own shared memory (no multicast).
+template <int STAGES>
+struct PairSmem {
+    static constexpr int A_BYTES = BM * BK * 2;              // this CTA's 128 rows of A
+    static constexpr int B_BYTES = BM * BK * 2;              // its half of the tile's 256 rows of B
+    static constexpr int STAGE = A_BYTES + B_BYTES;
+    static constexpr int BARS = STAGES * STAGE;              // full, peer_full, empty [S]; acc_full, acc_empty [2]
+    static constexpr int TMEM_SLOT = BARS + 8 * (3 * STAGES + 4);
+    static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;
+};
+constexpr int PAIR_BN = 256;
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
+gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
+                         const __grid_constant__ CUtensorMap bmap) {
+    using L = PairSmem<STAGES>;
+    constexpr int BN = PAIR_BN;
+    constexpr int TMEM_COLS = 2 * BN;                        // two accumulators of 256 columns
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (base - raw);
+    auto full = [&](int s) { return base + L::BARS + 8u * s; };
+    auto peer_full = [&](int s) { return base + L::BARS + 8u * (STAGES + s); };
+    auto empty = [&](int s) { return base + L::BARS + 8u * (2 * STAGES + s); };
+    auto acc_full = [&](int a) { return base + L::BARS + 8u * (3 * STAGES + a); };
+    auto acc_empty = [&](int a) { return base + L::BARS + 8u * (3 * STAGES + 2 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::TMEM_SLOT);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                    // 0: issues the instructions
+    const int m_pairs = (p.mm + 2 * BM - 1) / (2 * BM), n_tiles = (p.nn + BN - 1) / BN;
+    const int tile_count = m_pairs * n_tiles;
+    const int kblocks = (p.k + BK - 1) / BK;
+    const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+
+    chain_release();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full(s), 1);
+            mbar_init(peer_full(s), 1);
+            mbar_init(empty(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full(a), 1);
+            mbar_init(acc_empty(a), 8);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tc_fence_before();
+    cluster_sync_all();                  // both CTAs' barriers and tensor memory are ready
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool timed_out = false;
+    chain_wait();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int g = 0;
+            for (int tile = cluster; tile < tile_count && !timed_out; tile += clusters) {
+                const int mi = tile % m_pairs, ni = tile / m_pairs;
+                const int a_row = mi * 2 * BM + (int)rank * BM, b_row = ni * BN + (int)rank * BM;
+                for (int i = 0; i < kblocks; ++i, ++g) {
+                    const int slot = g % STAGES;
+                    if (!mbar_wait(empty(slot), ((g / STAGES) & 1) ^ 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    const uint32_t a_dst = base + slot * L::STAGE, b_dst = a_dst + L::A_BYTES;
+                    mbar_arrive_expect_tx(full(slot), L::STAGE);
+                    tma_load_2d(a_dst, &amap, i * BK, a_row, full(slot));
+                    tma_load_2d(b_dst, &bmap, i * BK, b_row, full(slot));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ----------------------------------------------- MMA issue for the pair
+            constexpr uint32_t idesc = umma_idesc_pair(BN);
+            int g = 0, it = 0;
+            for (int tile = cluster; tile < tile_count && !timed_out; tile += clusters, ++it) {
+                const int acc = it & 1;
+                if (!mbar_wait_cluster(acc_empty(acc), ((it >> 1) & 1) ^ 1)) {
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int i = 0; i < kblocks; ++i, ++g) {
+                    const int slot = g % STAGES;
+                    if (!mbar_wait(full(slot), (g / STAGES) & 1) ||
+                        !mbar_wait_cluster(peer_full(slot), (g / STAGES) & 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_src = base + slot * L::STAGE, b_src = a_src + L::A_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                        umma_pair(tmem_d, umma_desc(a_src + kk * UMMA_K * 2),
+                                  umma_desc(b_src + kk * UMMA_K * 2), idesc, (i | kk) ? 1u : 0u);
+                    umma_commit_pair(empty(slot), 3);        // both CTAs' stage is free
+                }
+                umma_commit_pair(acc_full(acc), 3);          // both CTAs' accumulator is complete
+            }
+        } else if (lane == 0) {
+            // ------------------ second CTA: tell the first that this CTA's stage has landed
+            int g = 0;
+            for (int tile = cluster; tile < tile_count && !timed_out; tile += clusters) {
+                for (int i = 0; i < kblocks; ++i, ++g) {
+                    const int slot = g % STAGES;
+                    if (!mbar_wait(full(slot), (g / STAGES) & 1)) {
+                        timed_out = true;
+                        break;
+                    }
+                    mbar_arrive_remote_relaxed(peer_full(slot), 0);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int q = warp & 3;
+        int it = 0;
+        for (int tile = cluster; tile < tile_count; tile += clusters, ++it) {
+            const int mi = tile % m_pairs, ni = tile / m_pairs;
+            const int acc = it & 1;
+            const int row = mi * 2 * BM + (int)rank * BM + q * 32 + lane;
+            if (!mbar_wait(acc_full(acc), (it >> 1) & 1)) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t ra[16], rb[16];
+                tmem_ld16(tmem_d + c0, ra);
+                tmem_ld16(tmem_d + c0 + 16, rb);
+                tmem_ld_wait();
+                float va[16], vb[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    va[e] = __uint_as_float(ra[e]);
+                    vb[e] = __uint_as_float(rb[e]);
+                }
+                const int col = ni * BN + c0;
+                if (p.epilogue == 1) {
+                    store_normal(p, row, col, va, vb);
+                } else {
+                    store_normal(p, row, col, va, va);
+                    store_normal(p, row, col + 16, vb, vb);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(acc_empty(acc));
+                else mbar_arrive_remote(acc_empty(acc), 0);
+            }
+        }
+    }
+    if (timed_out && p.status) atomicOr(p.status, MLS_STATUS_TIMEOUT);
+    __syncwarp();
+    tc_fence_before();
+    cluster_sync_all();                  // nobody of the pair touches tensor memory any more
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
 // Sum of the split-K parts, then the epilogue.  Parts are [part][row][col] in the
 // order the output has ([token][feature] in both orientations).
 __global__ void splitk_sum_kernel(const float* __restrict__ partial, void* __restrict__ out,
@@ -404,7 +593,43 @@ int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
                amap, bmap);
     return launch_status();
 }
+
+template <int STAGES>
+int launch_pair(const GemmParams& p, const void* a, const void* b, cudaStream_t stream) {
+    using L = PairSmem<STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap amap, bmap;
+    if (!operand_map(a, p.mm, p.k, BM, &amap) || !operand_map(b, p.nn, p.k, BM, &bmap))
+        return MLS_ERR_TENSOR_MAP;
+    const long long tiles = (long long)((p.mm + 2 * BM - 1) / (2 * BM)) *
+                            ((p.nn + PAIR_BN - 1) / PAIR_BN);
+    const long long most = sm_count() / 2;                   // one pair on two SMs
+    const int grid = 2 * (int)(tiles < most ? tiles : most);
+    MLS_LAUNCH((gemm_tcgen05_pair_kernel<STAGES>), dim3(grid), dim3(THREADS), L::TOTAL, stream, p,
+               amap, bmap);
+    return launch_status();
+}
+
+// Which kernel takes prompts of more than 128 rows when the package's own GEMM is asked
+// for: MLS_B200_GEMM_KERNEL = tiles (default: one CTA a tile of 128 x 256) or pair (two
+// CTAs a tile of 256 x 256).  Measured at 2,048 and 4,096 rows of the Llama-3-8B products
+// they run at the same speed (both are bound by what an SM's shared memory takes in and
+// gives out a k-block); the pair kernel reads a third less from L2.
+int g_prompt_kernel = [] {
+    const char* v = getenv("MLS_B200_GEMM_KERNEL");
+    return (v && v[0] == 'p') ? 1 : 0;
+}();
+
 }  // namespace
+
+// 0: prompts of more than 128 rows take one CTA a tile; 1: pairs of CTAs.
+MLS_API void mls_gemm_set_prompt_kernel(int which) { g_prompt_kernel = which ? 1 : 0; }
 
 // out[M, N] = act[M, K] * w[N, K]^T, bfloat16 operands, out bfloat16 or float32.
 // swap: 1 = the weights take the 128-row side (decoding, M <= 64).  splits > 1 cuts K
@@ -452,5 +677,6 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
     p.mm = m;
     p.nn = n;
     p.transposed = 0;
+    if (g_prompt_kernel == 1 && m > BM) return launch_pair<6>(p, act, w, stream);
     return launch<256, 4>(p, act, w, 1, stream);
 }
