@@ -336,22 +336,32 @@ gemm_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap
 // in its own tensor memory.
 //
 // Hand-overs inside the pair:
-//   full[s]       this CTA's TMA copies of stage s have landed (own barrier, byte count);
-//   peer_full[s]  (first CTA) the second CTA's copies of stage s have landed: its warp 1
-//                 waits on its own full[s] and arrives here across the cluster;
+//   full[s]       (first CTA) both CTAs' TMA copies of stage s have landed: the second CTA's
+//                 copies complete on the first CTA's barrier (the cta_group::2 form of the
+//                 load; forwarding the second CTA's own barrier by an arrival across the
+//                 cluster cost 0.03 us a k-block, a releasing arrival 0.5 us);
 //   empty[s]      the instructions reading stage s are done: tcgen05.commit arrives on
 //                 both CTAs' barriers at once;
 //   acc_full[a]   accumulator a is complete: commit to both CTAs;
 //   acc_empty[a]  (first CTA) both CTAs' epilogue warps have read accumulator a: four local
 //                 arrivals and four from the second CTA.
-// All loads are plain TMA loads into the CTA's own shared memory (no multicast).
+// Every load lands in the loading CTA's own shared memory only (no multicast).
+//
+// The epilogue (bfloat16 output whose rows are whole 16-byte chunks): the four epilogue
+// warps round 64 output columns of their 128 rows into a swizzled staging tile in shared
+// memory, and one thread hands the tile to TMA, which writes whole 128-byte row pieces and
+// clips at the matrix's edge; two staging tiles alternate.  (Storing from registers, each
+// thread 32 bytes of its own row, cost 7-10 % of the K = 4,096 products.)  Other outputs
+// are stored from registers.
 template <int STAGES>
 struct PairSmem {
     static constexpr int A_BYTES = BM * BK * 2;              // this CTA's 128 rows of A
     static constexpr int B_BYTES = BM * BK * 2;              // its half of the tile's 256 rows of B
     static constexpr int STAGE = A_BYTES + B_BYTES;
-    static constexpr int BARS = STAGES * STAGE;              // full, peer_full, empty [S]; acc_full, acc_empty [2]
-    static constexpr int TMEM_SLOT = BARS + 8 * (3 * STAGES + 4);
+    static constexpr int OUT_TILE = BM * 128;                // 128 rows of 64 bfloat16
+    static constexpr int OUT = STAGES * STAGE;               // two staging tiles
+    static constexpr int BARS = OUT + 2 * OUT_TILE;          // full, empty [S]; acc_full, acc_empty [2]
+    static constexpr int TMEM_SLOT = BARS + 8 * (2 * STAGES + 4);
     static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;
 };
 constexpr int PAIR_BN = 256;
@@ -359,7 +369,8 @@ constexpr int PAIR_BN = 256;
 template <int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
 gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
-                         const __grid_constant__ CUtensorMap bmap) {
+                         const __grid_constant__ CUtensorMap bmap,
+                         const __grid_constant__ CUtensorMap omap, int staged_stores) {
     using L = PairSmem<STAGES>;
     constexpr int BN = PAIR_BN;
     constexpr int TMEM_COLS = 2 * BN;                        // two accumulators of 256 columns
@@ -368,10 +379,9 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - raw);
     auto full = [&](int s) { return base + L::BARS + 8u * s; };
-    auto peer_full = [&](int s) { return base + L::BARS + 8u * (STAGES + s); };
-    auto empty = [&](int s) { return base + L::BARS + 8u * (2 * STAGES + s); };
-    auto acc_full = [&](int a) { return base + L::BARS + 8u * (3 * STAGES + a); };
-    auto acc_empty = [&](int a) { return base + L::BARS + 8u * (3 * STAGES + 2 + a); };
+    auto empty = [&](int s) { return base + L::BARS + 8u * (STAGES + s); };
+    auto acc_full = [&](int a) { return base + L::BARS + 8u * (2 * STAGES + a); };
+    auto acc_empty = [&](int a) { return base + L::BARS + 8u * (2 * STAGES + 2 + a); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L::TMEM_SLOT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -385,7 +395,6 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full(s), 1);
-            mbar_init(peer_full(s), 1);
             mbar_init(empty(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -416,9 +425,15 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                         break;
                     }
                     const uint32_t a_dst = base + slot * L::STAGE, b_dst = a_dst + L::A_BYTES;
-                    mbar_arrive_expect_tx(full(slot), L::STAGE);
-                    tma_load_2d(a_dst, &amap, i * BK, a_row, full(slot));
-                    tma_load_2d(b_dst, &bmap, i * BK, b_row, full(slot));
+                    if (rank == 0) {
+                        // both CTAs' copies of the stage complete on this barrier
+                        mbar_arrive_expect_tx(full(slot), 2 * L::STAGE);
+                        tma_load_2d(a_dst, &amap, i * BK, a_row, full(slot));
+                        tma_load_2d(b_dst, &bmap, i * BK, b_row, full(slot));
+                    } else {
+                        tma_load_2d_pair(a_dst, &amap, i * BK, a_row, full(slot));
+                        tma_load_2d_pair(b_dst, &bmap, i * BK, b_row, full(slot));
+                    }
                 }
             }
         }
@@ -437,8 +452,7 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                 const uint32_t tmem_d = tmem_base + acc * BN;
                 for (int i = 0; i < kblocks; ++i, ++g) {
                     const int slot = g % STAGES;
-                    if (!mbar_wait(full(slot), (g / STAGES) & 1) ||
-                        !mbar_wait_cluster(peer_full(slot), (g / STAGES) & 1)) {
+                    if (!mbar_wait_cluster(full(slot), (g / STAGES) & 1)) {
                         timed_out = true;
                         break;
                     }
@@ -452,34 +466,91 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                 }
                 umma_commit_pair(acc_full(acc), 3);          // both CTAs' accumulator is complete
             }
-        } else if (lane == 0) {
-            // ------------------ second CTA: tell the first that this CTA's stage has landed
-            int g = 0;
-            for (int tile = cluster; tile < tile_count && !timed_out; tile += clusters) {
-                for (int i = 0; i < kblocks; ++i, ++g) {
-                    const int slot = g % STAGES;
-                    if (!mbar_wait(full(slot), (g / STAGES) & 1)) {
-                        timed_out = true;
-                        break;
-                    }
-                    mbar_arrive_remote_relaxed(peer_full(slot), 0);
-                }
-            }
         }
     } else {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;
-        int it = 0;
+        const int row_in = q * 32 + lane;
+        const bool issuer = q == 0 && lane == 0;
+        const int acc_cols = p.epilogue == 1 ? 128 : 64;     // accumulator columns behind 64 outputs
+        int it = 0, fills = 0;
         for (int tile = cluster; tile < tile_count; tile += clusters, ++it) {
             const int mi = tile % m_pairs, ni = tile / m_pairs;
             const int acc = it & 1;
-            const int row = mi * 2 * BM + (int)rank * BM + q * 32 + lane;
+            const int row0 = mi * 2 * BM + (int)rank * BM;
+            const int row = row0 + row_in;
             if (!mbar_wait(acc_full(acc), (it >> 1) & 1)) {
                 timed_out = true;
                 break;
             }
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+            if (staged_stores) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += acc_cols, ++fills) {
+                    const uint32_t stage = base + L::OUT + (fills & 1) * L::OUT_TILE;
+                    // the store that last read this staging tile has read it
+                    if (issuer) tma_store_wait_read<1>();
+                    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+#pragma unroll
+                    for (int part = 0; part < 2; ++part) {   // 32 outputs each
+                        float r[32];
+                        if (p.epilogue == 1) {
+#pragma unroll
+                            for (int b = 0; b < 2; ++b) {    // 16 gate columns, then the 16 up columns
+                                uint32_t g[16], u[16];
+                                tmem_ld16(tmem_d + c0 + part * 64 + b * 32, g);
+                                tmem_ld16(tmem_d + c0 + part * 64 + b * 32 + 16, u);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int e = 0; e < 16; ++e)
+                                    r[b * 16 + e] = silu_mul(__uint_as_float(g[e]), __uint_as_float(u[e]));
+                            }
+                        } else {
+                            uint32_t a[16], b[16];
+                            tmem_ld16(tmem_d + c0 + part * 32, a);
+                            tmem_ld16(tmem_d + c0 + part * 32 + 16, b);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                r[e] = __uint_as_float(a[e]);
+                                r[16 + e] = __uint_as_float(b[e]);
+                            }
+                        }
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {     // 16-byte chunks of the row's 128 bytes
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(r[ch * 8 + 2 * e], r[ch * 8 + 2 * e + 1]);
+                                w[e] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            const int chunk = part * 4 + ch;
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
+                                         ::"r"(stage + row_in * 128 + (((chunk ^ (row_in & 7))) << 4)),
+                                           "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        }
+                    }
+                    if (c0 + acc_cols >= BN) {
+                        // the accumulator has been read: the MMA thread may fill it again
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (rank == 0) mbar_arrive(acc_empty(acc));
+                            else mbar_arrive_remote(acc_empty(acc), 0);
+                        }
+                    }
+                    fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                    if (issuer) {
+                        // a box that lies wholly outside the matrix is not handed over at all
+                        const int out_col = (ni * BN + c0) / (p.epilogue == 1 ? 2 : 1);
+                        const int width = p.epilogue == 1 ? p.nn / 2 : p.nn;
+                        if (row0 < p.mm && out_col < width) tma_store_2d(&omap, out_col, row0, stage);
+                    }
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t ra[16], rb[16];
@@ -507,6 +578,7 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                 else mbar_arrive_remote(acc_empty(acc), 0);
             }
         }
+        if (issuer) tma_store_wait_all();
     }
     if (timed_out && p.status) atomicOr(p.status, MLS_STATUS_TIMEOUT);
     __syncwarp();
@@ -572,6 +644,22 @@ bool operand_map(const void* ptr, long long rows, long long k, int box_rows, CUt
     return true;
 }
 
+// A map for storing [rows, cols] bfloat16 (rows ld elements apart) in boxes of 128 rows x 64.
+bool output_map(const void* ptr, long long rows, long long cols, long long ld, CUtensorMap* out) {
+    std::lock_guard<std::mutex> guard(g_lock);
+    MapKey key{ptr, rows, cols + (ld << 24), -BM};
+    auto it = g_maps.find(key);
+    if (it == g_maps.end()) {
+        if (g_maps.size() > 4096) g_maps.clear();
+        CUtensorMap m;
+        if (!make_map_bf16_2d(&m, ptr, (uint64_t)cols, (uint64_t)rows, (uint64_t)ld * 2, 64, BM))
+            return false;
+        it = g_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return true;
+}
+
 template <int BN, int STAGES>
 int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
            cudaStream_t stream) {
@@ -604,26 +692,34 @@ int launch_pair(const GemmParams& p, const void* a, const void* b, cudaStream_t 
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    CUtensorMap amap, bmap;
+    CUtensorMap amap, bmap, omap;
     if (!operand_map(a, p.mm, p.k, BM, &amap) || !operand_map(b, p.nn, p.k, BM, &bmap))
         return MLS_ERR_TENSOR_MAP;
+    // bfloat16 output with rows of whole 16-byte chunks goes out through shared memory and TMA
+    const int out_cols = p.epilogue == 1 ? p.nn / 2 : p.nn;
+    const int staged = (!p.out_f32 && p.ld_out % 8 == 0 &&
+                        (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) ? 1 : 0;
+    if (staged) {
+        if (!output_map(p.out, p.mm, out_cols, p.ld_out, &omap)) return MLS_ERR_TENSOR_MAP;
+    } else {
+        omap = amap;                                         // unused
+    }
     const long long tiles = (long long)((p.mm + 2 * BM - 1) / (2 * BM)) *
                             ((p.nn + PAIR_BN - 1) / PAIR_BN);
     const long long most = sm_count() / 2;                   // one pair on two SMs
     const int grid = 2 * (int)(tiles < most ? tiles : most);
     MLS_LAUNCH((gemm_tcgen05_pair_kernel<STAGES>), dim3(grid), dim3(THREADS), L::TOTAL, stream, p,
-               amap, bmap);
+               amap, bmap, omap, staged);
     return launch_status();
 }
 
-// Which kernel takes prompts of more than 128 rows when the package's own GEMM is asked
-// for: MLS_B200_GEMM_KERNEL = tiles (default: one CTA a tile of 128 x 256) or pair (two
-// CTAs a tile of 256 x 256).  Measured at 2,048 and 4,096 rows of the Llama-3-8B products
-// they run at the same speed (both are bound by what an SM's shared memory takes in and
-// gives out a k-block); the pair kernel reads a third less from L2.
+// Which kernel takes prompts of more than 128 rows: MLS_B200_GEMM_KERNEL = pair (default: two
+// CTAs a tile of 256 x 256) or tiles (one CTA a tile of 128 x 256).  Measured at 2,048 rows of
+// the Llama-3-8B products the pairs run at 1.33-1.39 PFLOP/s against 1.26-1.30 (with the
+// SwiGLU epilogue 1.45 against 1.43; at 512 rows 1.12 against 1.07).
 int g_prompt_kernel = [] {
     const char* v = getenv("MLS_B200_GEMM_KERNEL");
-    return (v && v[0] == 'p') ? 1 : 0;
+    return (v && v[0] == 't') ? 0 : 1;
 }();
 
 }  // namespace

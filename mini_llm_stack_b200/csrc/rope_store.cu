@@ -20,17 +20,27 @@
 // of every kv head) if the page's first slot was written in this step too.  Pages are
 // owned by one request, so "the next token has the next slot" means "same request", and
 // "the token `off` places back has this page's first slot" means the page was entered
-// in this step.  Called by all threads of one block per token, after chain_wait().
-template <typename T>
-__device__ __forceinline__ void clear_page_tail(const int* __restrict__ slot_map, int t,
-                                                int n_tokens, int slot, int block_size,
-                                                int n_pages, int n_kv, int hd,
-                                                T* __restrict__ k_pool, T* __restrict__ v_pool) {
-    const int page = slot / block_size, off = slot - page * block_size;
+// in this step.  Cleared by all threads of one block per token, after chain_wait().
+// How many slots after `slot` are to be cleared by token t's block (0: none).  Reads only
+// the step's slot map, which no kernel of the step writes: callers ask before chain_wait,
+// so that the two loads do not add to what follows the wait.
+__device__ __forceinline__ int page_tail_to_clear(const int* __restrict__ slot_map, int t,
+                                                  int n_tokens, int slot, int block_size) {
+    const int off = slot % block_size;
     const int rest = block_size - 1 - off;
+    if (rest <= 0 || slot < 0) return 0;
+    const int next = t + 1 < n_tokens ? slot_map[t + 1] : -1;
+    const int first = (off > 0 && t - off >= 0) ? slot_map[t - off] : -1;
+    if (next == slot + 1) return 0;                                     // not the last one
+    if (off > 0 && first != slot - off) return 0;                       // an older page
+    return rest;
+}
+template <typename T>
+__device__ __forceinline__ void clear_page_tail(int rest, int slot, int block_size, int n_pages,
+                                                int n_kv, int hd, T* __restrict__ k_pool,
+                                                T* __restrict__ v_pool) {
     if (rest <= 0) return;
-    if (t + 1 < n_tokens && slot_map[t + 1] == slot + 1) return;        // not the last one
-    if (off > 0 && (t - off < 0 || slot_map[t - off] != slot - off)) return;   // an older page
+    const int page = slot / block_size, off = slot - page * block_size;
     const size_t row_bytes = (size_t)hd * sizeof(T);
     if (row_bytes % 16 == 0) {
         const int chunks = (int)(row_bytes / 16) * rest;                 // per kv head and pool
@@ -105,8 +115,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
             const int kvh = u / hd, i = u - kvh * hd;
             v_pool[(((size_t)kvh * n_pages + page) * block_size + off) * hd + i] = vsrc[u];
         }
-        clear_page_tail<T>(slot_map, t, gridDim.x, slot, block_size, n_pages, n_kv, hd, k_pool,
-                           v_pool);
+        clear_page_tail<T>(page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size), slot,
+                           block_size, n_pages, n_kv, hd, k_pool, v_pool);
     }
 }
 
@@ -169,6 +179,8 @@ rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
     const bool slot_ok = slot >= 0 && slot < pool_slots;
     const int page = slot / block_size, off = slot - page * block_size;
     const int n_pages = pool_slots / block_size;
+    const int tail = (writes && slot_ok)
+                         ? page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size) : 0;
     chain_wait();
     if (threadIdx.x == 0 && status) {
         if (bad_pos) atomicOr(status, MLS_STATUS_BAD_POSITION);
@@ -215,9 +227,7 @@ rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                 v_pool + (((size_t)kvh * n_pages + page) * block_size + off) * hd + c * N) = raw;
         }
     }
-    if (writes && slot_ok)
-        clear_page_tail<T>(slot_map, t, gridDim.x, slot, block_size, n_pages, n_kv, hd, k_pool,
-                           v_pool);
+    clear_page_tail<T>(tail, slot, block_size, n_pages, n_kv, hd, k_pool, v_pool);
 }
 
 // Four values rounded to bfloat16, as floats again / as the eight bytes to store.
@@ -267,6 +277,8 @@ rope_store_parts_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__
     const int v_units = writes ? n_kv * (hd / 4) : 0;
     const int per_block = (rot_units + v_units + gridDim.y - 1) / gridDim.y;
     const int u_end = min(rot_units + v_units, (int)(blockIdx.y + 1) * per_block);
+    const int tail = (writes && slot_ok && blockIdx.y == gridDim.y - 1)
+                         ? page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size) : 0;
     chain_wait();
     if (threadIdx.x == 0 && blockIdx.y == 0 && status) {
         if (bad_pos) atomicOr(status, MLS_STATUS_BAD_POSITION);
@@ -314,9 +326,7 @@ rope_store_parts_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__
                 pack_bf16x4(x[0]);
         }
     }
-    if (writes && slot_ok && blockIdx.y == 0)
-        clear_page_tail<__nv_bfloat16>(slot_map, t, gridDim.x, slot, block_size, n_pages, n_kv, hd,
-                                       k_pool, v_pool);
+    clear_page_tail<__nv_bfloat16>(tail, slot, block_size, n_pages, n_kv, hd, k_pool, v_pool);
 }
 
 MLS_API int mls_rope_store(void* qkv, int dtype, const int* positions, const float* cos_t,

@@ -149,6 +149,36 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// The same from a CTA of a pair (cta_group::2) whose copy completes on the barrier at the
+// same offset in the pair's first CTA: the first CTA's instruction thread then waits on
+// one barrier for both CTAs' halves of a stage.  No multicast: the box lands in this CTA's
+// own shared memory only.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .b32 rbar;\n\t"
+        "mapa.shared::cluster.u32 rbar, %2, 0;\n\t"
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [rbar];\n\t}"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+// One box from shared memory to a 2-D tensor map (what lies outside the tensor is not
+// written).  Stores of a thread form groups; `tma_store_wait_read<N>` returns when all but
+// the last N groups have read their shared memory, `tma_store_wait_all` when all are written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+        "cp.async.bulk.commit_group;\n"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+}
 // A contiguous run of bytes into shared memory (both addresses and the size are
 // multiples of 16); completion is counted in bytes on the mbarrier.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,

@@ -133,7 +133,7 @@ class Ops:
         self._tc_rows: dict = {}                 # head size -> rows of a tile of the tcgen05 kernel
         self._scratch: dict = {}
         self._gemm = None
-        self._pair_set = False
+        self._tiles_set = False
         self._parts_busy = False
         self.attention_impl = os.environ.get("MLS_B200_ATTENTION", "auto")
         self.gemm_impl = os.environ.get("MLS_B200_GEMM", "auto")
@@ -280,11 +280,12 @@ class Ops:
 
     def _use_own_gemm(self, m: int, n: int, k: int) -> bool:
         """The tcgen05 kernel takes rows that are whole 16-byte chunks; the choice
-        between it and the library is ``MLS_B200_GEMM`` (tcgen05 | tcgen05-pair | cublas |
-        auto; ``tcgen05-pair`` runs prompts of more than 128 rows on pairs of CTAs)."""
+        between it and the library is ``MLS_B200_GEMM`` (tcgen05 | tcgen05-tiles | cublas |
+        auto; prompts of more than 128 rows run on pairs of CTAs, with ``tcgen05-tiles``
+        on one CTA a tile)."""
         if self.gemm_impl == "cublas" or k % 8 != 0:
             return False
-        if self.gemm_impl in ("tcgen05", "tcgen05-pair"):
+        if self.gemm_impl in ("tcgen05", "tcgen05-tiles"):
             return True
         # auto: a few rows (decoding) go to the tcgen05 kernel, which asks for its
         # first weights while the kernel before it still runs; more rows go to the
@@ -311,12 +312,12 @@ class Ops:
             self._gemm = _decl(lib, "mls_gemm_bf16",
                                [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P])
             self._gemm_lib = lib
-        if self.gemm_impl == "tcgen05-pair" or self._pair_set:
-            # prompts of more than 128 rows on pairs of CTAs (tiles of 256 x 256)
+        if self.gemm_impl == "tcgen05-tiles" or self._tiles_set:
+            # prompts of more than 128 rows on one CTA a tile instead of pairs of CTAs
             self._gemm_lib.mls_gemm_set_prompt_kernel.argtypes = [_I]
             self._gemm_lib.mls_gemm_set_prompt_kernel.restype = None
-            self._pair_set = self.gemm_impl == "tcgen05-pair"
-            self._gemm_lib.mls_gemm_set_prompt_kernel(1 if self._pair_set else 0)
+            self._tiles_set = self.gemm_impl == "tcgen05-tiles"
+            self._gemm_lib.mls_gemm_set_prompt_kernel(0 if self._tiles_set else 1)
         swap = 1 if m <= 64 else 0
         splits, partial = 1, None
         if swap:

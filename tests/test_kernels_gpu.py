@@ -147,12 +147,12 @@ def test_linear_with_float32_weights_in_a_bfloat16_run(rts):
                                      # row counts whose 128-row tiles do not fill whole rounds of
                                      # CTAs: tiles of 96 + 128 rows, and of 64 + 96
                                      (2, 128256, 128), (5, 22016, 256), (64, 28672, 64),
-                                     # more than 128 rows ("tcgen05-pair": pairs of CTAs on tiles of
-                                     # 256 x 256), ragged edges in every dimension, many tiles a CTA
+                                     # more than 128 rows (pairs of CTAs on tiles of 256 x 256, or with
+                                     # "tcgen05-tiles" one CTA a tile), ragged edges, many tiles a CTA
                                      (257, 513, 136), (600, 1000, 4096), (512, 6144, 4096),
                                      (2048, 4096, 4096), (130, 40, 64)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05-pair", "cublas"])
+@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05-tiles", "cublas"])
 def test_linear_bf16(rts, m, n, k, out_dtype, impl):
     ops = rts[torch.bfloat16].ops
     a, w = rand((m, k), torch.bfloat16, 12), rand((n, k), torch.bfloat16, 13, 0.05)
