@@ -24,6 +24,7 @@ weights).  The line names it in ``config.kv_heads``.
 from __future__ import annotations
 
 import json
+import os
 import shutil
 import sys
 import time
@@ -32,7 +33,9 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 TREE = HERE / "_ref"
-SOURCES = (Path("/root/reference"),)
+# where a checkout of the reference may lie: named by the environment, or beside this repository
+SOURCES = tuple(Path(p) for p in (os.environ.get("MLS_REFERENCE_TREE"),
+                                  HERE.parent.parent / "reference") if p)
 
 SHAPE = dict(vocab_size=128256, d_model=4096, n_layers=32, n_heads=32, max_seq_len=8192,
              rope_theta=500000.0, norm_eps=1e-5, tie_embeddings=False, ffn_mult=5.25)
