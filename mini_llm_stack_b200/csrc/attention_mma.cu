@@ -55,6 +55,26 @@ struct Params {
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
 };
 
+// What the split kernel needs to take the rotation and the cache write upon itself in a
+// step of single decoded tokens (parts == nullptr: it does not).  The q/k/v projection is
+// then read as the float32 K-parts of its matrix product ([n_parts][T][(H + 2 Hkv) * HD]);
+// every CTA adds up, rounds and rotates the queries of its kv head's group, and the CTA whose
+// stretch of the context holds the new token does the same for the new key and value,
+// writes them to their slot of the cache and into its own tile of keys and values in shared
+// memory (the copy of that page from memory may have been made before the write).
+struct Fused {
+    const float* parts;
+    int n_parts;
+    long long part_stride;
+    const int* positions;                // [T]
+    const float* cos_t;                  // [max_pos, HD / 2]
+    const float* sin_t;
+    const int* slot_map;                 // [T]
+    __nv_bfloat16* k_out;                // the pools, writable
+    __nv_bfloat16* v_out;
+    int max_pos, writes;
+};
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -643,7 +663,8 @@ __device__ __forceinline__ void produce_tiles(const Params& P, const CUtensorMap
 }
 
 __global__ void __launch_bounds__(TMA_THREADS)
-attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
+attention_split_tma_kernel(const Params P, const Fused F,
+                           const __grid_constant__ CUtensorMap kmap,
                            const __grid_constant__ CUtensorMap vmap,
                            const __grid_constant__ CUtensorMap kmap_wide,
                            const __grid_constant__ CUtensorMap vmap_wide) {
@@ -717,7 +738,90 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
     uint32_t qf[HD / 16][4];
 
-    if (n_tiles > 0) {
+    // fused rotation (single decoded tokens): this CTA's queries from the projection's parts,
+    // and, in the CTA whose tiles end at the new token, the new key and value
+    const bool fused = F.parts != nullptr;
+    const bool owns_new = fused && F.writes && n_tiles > 0 && t_end == tiles_all;
+    uint2 new_kv[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};     // this thread's share of them
+    if (fused && n_tiles > 0) {
+        constexpr int half = HD / 2, qph = half / 4;
+        int pos = F.positions[tok0];
+        if (pos < 0 || pos >= F.max_pos || q_len != 1) {
+            if (threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_POSITION);
+            pos = pos < 0 ? 0 : (pos >= F.max_pos ? F.max_pos - 1 : pos);
+        }
+        const float* cr = F.cos_t + (size_t)pos * half;
+        const float* sr = F.sin_t + (size_t)pos * half;
+        const size_t width = (size_t)(P.n_heads + 2 * P.n_kv) * HD;
+        const size_t row_at = (size_t)tok0 * width;
+        for (int u = threadIdx.x; u < 16 * qph; u += 128) {
+            const int g = u / qph, c = u - g * qph;
+            uint2 w1 = make_uint2(0u, 0u), w2 = w1;
+            if (g < rows) {
+                const size_t col = (size_t)(kvh * P.group + g) * HD + c * 4;
+                const size_t at[2] = {row_at + col, row_at + col + half};
+                float4 x[2], o1, o2;
+                sum_parts4_of<2, 8>(F.parts, at, F.n_parts, (size_t)F.part_stride, x);
+                rotate_half4(round_bf16(x[0]), round_bf16(x[1]),
+                             *reinterpret_cast<const float4*>(cr + c * 4),
+                             *reinterpret_cast<const float4*>(sr + c * 4), o1, o2);
+                w1 = pack_bf16x4(o1);
+                w2 = pack_bf16x4(o2);
+            }
+            const uint32_t dst = q_addr + g * ROWB + c * 8;
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(dst), "r"(w1.x), "r"(w1.y) : "memory");
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(dst + half * 2), "r"(w2.x), "r"(w2.y)
+                         : "memory");
+        }
+        if (owns_new) {
+            // threads 0 .. qph-1: four rotated pairs of the key each; the next HD / 4: four
+            // values of the value each.  Into the cache now, into the tile when it has landed.
+            const int slot = F.slot_map[tok0];
+            const long long pool_slots = P.n_pages * P.block_size;
+            const bool slot_ok = slot >= 0 && slot < pool_slots;
+            if (!slot_ok && threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_SLOT);
+            const int page = slot_ok ? slot / P.block_size : 0;
+            const int off = slot_ok ? slot - page * P.block_size : 0;
+            const size_t cache_at = (((size_t)kvh * P.n_pages + page) * P.block_size + off) * HD;
+            const int u = threadIdx.x;
+            if (u < qph) {
+                const size_t col = (size_t)(P.n_heads + kvh) * HD + u * 4;
+                const size_t at[2] = {row_at + col, row_at + col + half};
+                float4 x[2], o1, o2;
+                sum_parts4_of<2, 8>(F.parts, at, F.n_parts, (size_t)F.part_stride, x);
+                rotate_half4(round_bf16(x[0]), round_bf16(x[1]),
+                             *reinterpret_cast<const float4*>(cr + u * 4),
+                             *reinterpret_cast<const float4*>(sr + u * 4), o1, o2);
+                new_kv[0] = pack_bf16x4(o1);
+                new_kv[1] = pack_bf16x4(o2);
+                if (slot_ok) {
+                    *reinterpret_cast<uint2*>(F.k_out + cache_at + u * 4) = new_kv[0];
+                    *reinterpret_cast<uint2*>(F.k_out + cache_at + half + u * 4) = new_kv[1];
+                }
+            } else if (u < qph + HD / 4) {
+                const int c = u - qph;
+                const size_t at[1] = {row_at + (size_t)(P.n_heads + P.n_kv + kvh) * HD + c * 4};
+                float4 x[1];
+                sum_parts4_of<1, 8>(F.parts, at, F.n_parts, (size_t)F.part_stride, x);
+                new_kv[0] = pack_bf16x4(x[0]);
+                if (slot_ok) *reinterpret_cast<uint2*>(F.v_out + cache_at + c * 4) = new_kv[0];
+            }
+            // a page that this token enters: what its previous owner left in the other slots
+            // must not reach a later step as 0 * NaN
+            if (slot_ok && off == 0 && P.block_size > 1) {
+                const int chunks = (P.block_size - 1) * (HD / 8);
+                for (int i = threadIdx.x; i < 2 * chunks; i += 128) {
+                    __nv_bfloat16* pool = i < chunks ? F.k_out : F.v_out;
+                    reinterpret_cast<uint4*>(pool + cache_at + HD)[i < chunks ? i : i - chunks] =
+                        make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        const uint32_t qa = q_addr + ((lane & 7) + ((lane >> 3) & 1) * 8) * ROWB + (lane >> 4) * 16;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) ldsm_x4(qf[ks], qa + ks * 32);
+    } else if (n_tiles > 0) {
         // the queries: plain asynchronous copies into a padded tile, then registers
         const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
         for (int idx = threadIdx.x; idx < 16 * KCH; idx += 128) {
@@ -749,6 +853,35 @@ attention_split_tma_kernel(const Params P, const __grid_constant__ CUtensorMap k
         const uint32_t ktile = base + slot * KV_STAGE;
         const uint32_t vtile = ktile + HALVES * HALF_BYTES;
         const int kbase = kbase0 + (t_begin + t) * BN + warp * 16;
+        if (owns_new && t == n_tiles - 1) {
+            // the new token's key and value over whatever the page held when it was copied
+            constexpr int half = HD / 2, qph = half / 4;
+            const int row = pos0 - (kbase0 + (t_begin + t) * BN);
+            const int u = threadIdx.x;
+            if (u < qph) {
+                const uint32_t a = swz(ktile, row, (u * 4) >> 3) + ((u * 4) & 7) * 2;
+                const uint32_t b = swz(ktile, row, (half + u * 4) >> 3) + ((half + u * 4) & 7) * 2;
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(a), "r"(new_kv[0].x),
+                             "r"(new_kv[0].y) : "memory");
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(b), "r"(new_kv[1].x),
+                             "r"(new_kv[1].y) : "memory");
+            } else if (u < qph + HD / 4) {
+                const int c = u - qph;
+                const uint32_t a = swz(vtile, row, (c * 4) >> 3) + ((c * 4) & 7) * 2;
+                asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(a), "r"(new_kv[0].x),
+                             "r"(new_kv[0].y) : "memory");
+            }
+            // the rows after it are no keys yet: whatever the page held when it was copied
+            // (this CTA clears a page it enters in memory, but the copy may have come first)
+            // must not meet a probability of zero as NaN
+            for (int i = threadIdx.x; i < (BN - 1 - row) * KCH * 2; i += 128) {
+                const int which = i / ((BN - 1 - row) * KCH), w = i - which * (BN - 1 - row) * KCH;
+                const int rr = row + 1 + w / KCH, ch = w - (w / KCH) * KCH;
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n"
+                             ::"r"(swz(which ? vtile : ktile, rr, ch)), "r"(0u) : "memory");
+            }
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        }
 
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
@@ -1218,7 +1351,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
 #if MLS_HEAD_DIM % 64 == 0
         if (tma_ok)
             MLS_LAUNCH((attention_split_tma_kernel), dim3(n_req, n_kv, n_split), dim3(TMA_THREADS),
-                       TMA_SMEM, stream, P, kmap, vmap, kmap_wide, vmap_wide);
+                       TMA_SMEM, stream, P, Fused{}, kmap, vmap, kmap_wide, vmap_wide);
         else
 #endif
             MLS_LAUNCH((attention_split_kernel), dim3(n_req, n_kv, n_split), dim3(NT), SPLIT_SMEM,
@@ -1234,6 +1367,87 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
         }
     }
     return 0;
+}
+
+// A step of single decoded tokens (one token a request) with the rotation and the cache
+// write inside the attention kernel: q, k and v are read as the n_parts float32 K-parts of
+// their projection ([n_parts][n_req][(H + 2 Hkv) * HD], part_stride elements apart), rotated
+// by the rows of cos / sin at positions[t]; with `writes` the rotated key and the value go to
+// slot_map[t] of the pools.  Otherwise as mls_attention_mma with every request small.
+// Head sizes that are multiples of 64 and pages of 8, 16, 32 or 64 only (else
+// MLS_ERR_UNSUPPORTED and nothing is launched).
+MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long long part_stride,
+                                       const int* positions, const float* cos_t,
+                                       const float* sin_t, int max_pos, const int* slot_map,
+                                       int writes, void* out, void* k_pool, void* v_pool,
+                                       const int* block_table, int max_blocks, const int* cu_q,
+                                       const int* ctx_len, int n_req, int n_heads, int n_kv,
+                                       int block_size, float scale, int window, int n_split,
+                                       float* part_o, float* part_lse, long long pool_pages,
+                                       int* status, cudaStream_t stream) {
+#if MLS_HEAD_DIM % 64 == 0
+    if (n_req <= 0) return 0;
+    if (n_heads % n_kv || n_heads / n_kv > 16 || n_split < 1 || n_split > MAX_SPLITS ||
+        (n_split > 1 && (!part_o || !part_lse)) || !parts || n_parts < 1 || part_stride % 4 != 0)
+        return MLS_ERR_UNSUPPORTED;
+    if (!(block_size == 8 || block_size == 16 || block_size == 32 || block_size == 64))
+        return MLS_ERR_UNSUPPORTED;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_split_tma_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, TMA_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap kmap, vmap, kmap_wide, vmap_wide;
+    const long long rows = pool_pages * n_kv * block_size;
+    if (!pool_map(k_pool, rows, block_size, &kmap) || !pool_map(v_pool, rows, block_size, &vmap) ||
+        !pool_map(k_pool, rows, BN, &kmap_wide) || !pool_map(v_pool, rows, BN, &vmap_wide))
+        return MLS_ERR_TENSOR_MAP;
+    Params P;
+    P.qkv = nullptr;
+    P.out = (__nv_bfloat16*)out;
+    P.k_pool = (const __nv_bfloat16*)k_pool;
+    P.v_pool = (const __nv_bfloat16*)v_pool;
+    P.block_table = block_table;
+    P.cu_q = cu_q;
+    P.ctx_len = ctx_len;
+    P.part_o = part_o;
+    P.part_lse = part_lse;
+    P.max_blocks = max_blocks;
+    P.n_req = n_req;
+    P.n_tokens = n_req;
+    P.n_heads = n_heads;
+    P.n_kv = n_kv;
+    P.group = n_heads / n_kv;
+    P.block_size = block_size;
+    P.window = window;
+    P.n_split = n_split;
+    P.small_only = 1;
+    P.scale_log2 = scale * LOG2E;
+    P.status = status;
+    P.n_pages = pool_pages;
+    Fused F;
+    F.parts = parts;
+    F.n_parts = n_parts;
+    F.part_stride = part_stride;
+    F.positions = positions;
+    F.cos_t = cos_t;
+    F.sin_t = sin_t;
+    F.slot_map = slot_map;
+    F.k_out = (__nv_bfloat16*)k_pool;
+    F.v_out = (__nv_bfloat16*)v_pool;
+    F.max_pos = max_pos;
+    F.writes = writes ? 1 : 0;
+    MLS_LAUNCH((attention_split_tma_kernel), dim3(n_req, n_kv, n_split), dim3(TMA_THREADS), TMA_SMEM,
+               stream, P, F, kmap, vmap, kmap_wide, vmap_wide);
+    if (n_split > 1)
+        MLS_LAUNCH((attention_merge_kernel), dim3(n_req, n_heads),
+                   dim3(HD < 32 ? 32 : (HD < 128 ? HD : 128)), 0, stream, P);
+    return launch_status();
+#else
+    return MLS_ERR_UNSUPPORTED;
+#endif
 }
 
 MLS_API int mls_attention_head_dim() { return HD; }

@@ -131,6 +131,35 @@ static __device__ __forceinline__ void sum_parts4_of(const float* __restrict__ b
     }
 }
 
+// Four values rounded to bfloat16, as floats again / as the eight bytes to store.
+static __device__ __forceinline__ float4 round_bf16(float4 v) {
+    return make_float4(__bfloat162float(__float2bfloat16_rn(v.x)),
+                       __bfloat162float(__float2bfloat16_rn(v.y)),
+                       __bfloat162float(__float2bfloat16_rn(v.z)),
+                       __bfloat162float(__float2bfloat16_rn(v.w)));
+}
+static __device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
+    uint2 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(v.x, v.y);
+    h[1] = __floats2bfloat162_rn(v.z, v.w);
+    return raw;
+}
+// Rotate-half of four pairs (x1 from the first half of a head, x2 from the second), as the
+// reference's expression: o1 = x1*c - x2*s, o2 = x2*c + x1*s, products and sums separate
+// float32 operations (train/model.py:47-52).
+static __device__ __forceinline__ void rotate_half4(float4 x1, float4 x2, float4 cs, float4 sn,
+                                                    float4& o1, float4& o2) {
+    o1.x = __fsub_rn(__fmul_rn(x1.x, cs.x), __fmul_rn(x2.x, sn.x));
+    o1.y = __fsub_rn(__fmul_rn(x1.y, cs.y), __fmul_rn(x2.y, sn.y));
+    o1.z = __fsub_rn(__fmul_rn(x1.z, cs.z), __fmul_rn(x2.z, sn.z));
+    o1.w = __fsub_rn(__fmul_rn(x1.w, cs.w), __fmul_rn(x2.w, sn.w));
+    o2.x = __fadd_rn(__fmul_rn(x2.x, cs.x), __fmul_rn(x1.x, sn.x));
+    o2.y = __fadd_rn(__fmul_rn(x2.y, cs.y), __fmul_rn(x1.y, sn.y));
+    o2.z = __fadd_rn(__fmul_rn(x2.z, cs.z), __fmul_rn(x1.z, sn.z));
+    o2.w = __fadd_rn(__fmul_rn(x2.w, cs.w), __fmul_rn(x1.w, sn.w));
+}
+
 // Streaming multiprocessors of the current device (148 on a B200), asked once.
 static inline int sm_count() {
     static const int n = [] {

@@ -230,21 +230,6 @@ rope_store_vec_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
     clear_page_tail<T>(tail, slot, block_size, n_pages, n_kv, hd, k_pool, v_pool);
 }
 
-// Four values rounded to bfloat16, as floats again / as the eight bytes to store.
-__device__ __forceinline__ float4 round_bf16(float4 v) {
-    return make_float4(__bfloat162float(__float2bfloat16_rn(v.x)),
-                       __bfloat162float(__float2bfloat16_rn(v.y)),
-                       __bfloat162float(__float2bfloat16_rn(v.z)),
-                       __bfloat162float(__float2bfloat16_rn(v.w)));
-}
-__device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
-    uint2 raw;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-    h[0] = __floats2bfloat162_rn(v.x, v.y);
-    h[1] = __floats2bfloat162_rn(v.z, v.w);
-    return raw;
-}
-
 // The rows are still in the parts a matrix product was cut into along K (float32
 // [n_parts][tokens][row width]): a thread adds up four values of each half of a head
 // in the order of the parts, rounds them to bfloat16 as the finished product would

@@ -130,6 +130,7 @@ class Ops:
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
+        self._attention_fused: dict = {}         # head size -> decode attention that also rotates
         self._tc_rows: dict = {}                 # head size -> rows of a tile of the tcgen05 kernel
         self._scratch: dict = {}
         self._gemm = None
@@ -423,6 +424,10 @@ class Ops:
                         _P, _P, _LL, _P, _I, _P])
             tc = _decl(lib, "mls_attention_tc",
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _LL, _P, _P])
+            fused = _decl(lib, "mls_attention_decode_fused",
+                          [_P, _I, _LL, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I,
+                           _I, _I, _F, _I, _I, _P, _P, _LL, _P, _P])
+            self._attention_fused[hd] = fused
             rows_fn = lib.mls_attention_tc_rows
             rows_fn.restype = ctypes.c_int
             self._tc_rows[hd] = int(rows_fn()) or 128
@@ -489,6 +494,49 @@ class Ops:
             _ptr(g.block_table), g.max_blocks, _ptr(step.positions), _ptr(step.req_of_token),
             t, n_heads, n_kv, hd, g.block_size, float(scale), int(window),
             cache.k_pool.shape[1], self._stream()), "attention_simt")
+
+    def can_fuse_rope_attention(self, hd: int, block_size: int) -> bool:
+        """Whether a step of single decoded tokens can leave the rotation and the cache
+        write to the attention kernel (``attention_decode_fused``)."""
+        return (self.act_dtype == torch.bfloat16 and self.attention_impl == "auto"
+                and hd % 64 == 0 and block_size in (8, 16, 32, 64)
+                and os.environ.get("MLS_B200_FUSED_ROPE", "1") != "0")
+
+    def attention_decode_fused(self, parts, out, cache, step, cos, sin, max_pos: int,
+                               n_heads: int, n_kv: int, hd: int, scale: float, window: int,
+                               plan) -> None:
+        """A step of one token a request: rotate q and k (read as the K-parts of their
+        projection), store k and v, attend.  One kernel (and the merge of the context
+        splits) instead of ``rope_store`` + ``paged_attention``; the bits are the same."""
+        g = step.groups[cache.group]
+        t = step.n_tokens
+        width = (n_heads + 2 * n_kv) * hd
+        _need(step.max_q_len == 1 and t == step.n_requests, "fused attention: single tokens only")
+        _need(isinstance(parts, SplitParts) and tuple(parts.shape) == (t, width)
+              and parts.parts.is_contiguous(), "fused attention: bad parts")
+        _need(out.shape == (t, n_heads * hd) and out.is_contiguous()
+              and out.dtype == torch.bfloat16, "fused attention: bad out")
+        _need(cache.k_pool.dtype == torch.bfloat16 and cache.k_pool.is_contiguous()
+              and cache.v_pool.is_contiguous(), "fused attention: pool layout")
+        _need(cos.shape == (max_pos, hd // 2) and cos.dtype == torch.float32, "fused attention: tables")
+        fn = self._attention_fused.get(hd)
+        _need(fn is not None and plan is not None, "fused attention: kernels were not required")
+        n_split = plan.n_split
+        part_o = part_lse = None
+        if n_split > 1:
+            units = t * n_heads
+            scratch = self.scratch("attention_partials", n_split * units * (hd + 1))
+            part_o = scratch[:n_split * units * hd]
+            part_lse = scratch[n_split * units * hd:]
+        self.launches += 2 if n_split > 1 else 1
+        _check(fn(parts.parts.data_ptr(), parts.parts.shape[0], t * width, _ptr(step.positions),
+                  _ptr(cos), _ptr(sin), max_pos, _ptr(g.slot_map), 1 if cache.writes else 0,
+                  _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool), _ptr(g.block_table),
+                  g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len), step.n_requests, n_heads,
+                  n_kv, g.block_size, float(scale), int(window), n_split, _ptr(part_o),
+                  _ptr(part_lse), cache.k_pool.shape[1], _ptr(self.status), self._stream()),
+               "attention_decode_fused")
+        parts.release()
 
     def swiglu(self, gu, out) -> None:
         t, inter = out.shape

@@ -135,17 +135,29 @@ class GroupedQueryAttention(Mixer):
         hd = self.head_dim
         width = (self.n_heads + 2 * self.n_kv_heads) * hd
         qkv = rt.buffer("qkv", (t, width), rt.act_dtype)
+        o = rt.buffer("attn_out", (t, self.n_heads * hd), rt.act_dtype)
         if getattr(self.position, "takes_parts", False):
             # the projection may stay in the parts it was cut into along K: the
             # rotation adds them up as it reads them
             src = rt.ops.linear_parts(h, self.wqkv, qkv)
+            tables = (self.position.fused_tables()
+                      if src is not qkv and step.max_q_len == 1 and cache.kind == "paged"
+                      and hasattr(self.position, "fused_tables") else None)
+            if tables is not None and rt.ops.can_fuse_rope_attention(
+                    hd, step.groups[cache.group].block_size):
+                # single decoded tokens: the attention kernel rotates and stores as well
+                cos, sin, max_pos = tables
+                rt.ops.attention_decode_fused(src, o, cache, step, cos, sin, max_pos,
+                                              self.n_heads, self.n_kv_heads, hd, self.scale,
+                                              self.window or 0, self.plan(step))
+                delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
+                return rt.ops.linear_parts(o, self.wo, delta)
             self.position.rotate_and_store(qkv, step, cache, self.n_heads, self.n_kv_heads,
                                            parts=None if src is qkv else src)
         else:
             rt.ops.linear(h, self.wqkv, qkv)
             self.position.rotate_and_store(qkv, step, cache, self.n_heads,
                                            self.n_kv_heads)
-        o = rt.buffer("attn_out", (t, self.n_heads * hd), rt.act_dtype)
         rt.ops.paged_attention(qkv, o, cache, step, self.n_heads, self.n_kv_heads,
                                hd, self.scale, self.window or 0, plan=self.plan(step))
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)

@@ -47,6 +47,12 @@ class RotaryPosition(PositionEncoding):
         parts of a cut along K) in place of filled ``qkv`` rows."""
         return self.runtime.ops.rope_takes_parts(self.head_dim)
 
+    def fused_tables(self):
+        """(cos, sin, max_positions) for a mixer whose kernel rotates by table row itself
+        (rotate-half of q and k, k and v stored at the step's slots), or None if this
+        encoding cannot be applied that way."""
+        return self.cos, self.sin, self.max_positions
+
     def rotate_and_store(self, qkv, step: StepContext, cache: CacheHandle,
                          n_heads: int, n_kv_heads: int, parts=None) -> None:
         """Rotate q and k of ``qkv`` in place; store rotated k and raw v.

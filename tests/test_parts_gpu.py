@@ -178,6 +178,60 @@ def test_what_a_page_held_before_does_not_reach_its_next_owner(rts, dtype, heads
     assert close(got, want, dtype)
 
 
+@pytest.mark.parametrize("heads, kv, hd, d, window, block", [(4, 2, 64, 1024, None, 16),
+                                                             (8, 2, 128, 1024, None, 16),
+                                                             (8, 2, 128, 1024, 150, 8),
+                                                             (32, 8, 128, 4096, None, 16)])
+def test_decode_attention_that_rotates_and_stores_itself_gives_the_same_bits(
+        rts, monkeypatch, heads, kv, hd, d, window, block):
+    """Single decoded tokens: the attention kernel reads q, k and v as the K-parts of their
+    projection, rotates, writes the cache and attends.  Outputs and pools must be, bit for
+    bit, what the rotation kernel followed by the attention kernel gives; requests of
+    different lengths, tokens that enter a page, a pool that held NaN before."""
+    rt = rts[torch.bfloat16]
+
+    def run(fused):
+        monkeypatch.setenv("MLS_B200_FUSED_ROPE", "1" if fused else "0")
+        pos = RotaryPosition(hd, 10000.0, 2048)
+        mixer = GroupedQueryAttention(d, heads, kv, hd, hd ** -0.5, pos, window=window)
+        mixer.bind(draw(mixer, torch.bfloat16, 25), rt)
+        cache = CacheManager([mixer.cache_spec()], 300, block, 4, 2048, device=DEV,
+                             kv_dtype=torch.bfloat16)
+        cache.paged[0].kv.fill_(float("nan"))
+        handle = cache.handles()[0]
+        g = torch.Generator(device=DEV).manual_seed(3)
+        lens = {"a": 700, "b": 31, "c": 1290}
+        outs = []
+        for r, n in lens.items():                      # the prompts, one request a step
+            h = (torch.randn(n, d, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+            step = step_for(cache, [(r, [0] * n)])
+            mixer.forward(h, step, handle).float()     # (a product left as parts is given back)
+            cache.commit(r, n)
+        used = []
+        for i in range(20):                            # decoded tokens, all three a step
+            h = (torch.randn(3, d, device=DEV, generator=g) * 0.5).to(torch.bfloat16)
+            step = step_for(cache, [(r, [0]) for r in lens])
+            before = rt.ops.launches
+            out = mixer.forward(h, step, handle)
+            outs.append(out.float().clone())
+            used.append(rt.ops.launches - before)
+            for r in lens:
+                cache.commit(r, 1)
+        rt.ops.check_status()
+        live = cache.paged[0].kv.clone()
+        return torch.stack(outs), live, used
+
+    fused, pool_f, n_f = run(True)
+    plain, pool_p, n_p = run(False)
+    assert max(n_f) < max(n_p)                         # one kernel fewer a step
+    assert bool(torch.isfinite(fused).all())
+    assert torch.equal(fused, plain)
+    # the pools agree wherever a request's key or value lies (the rest is NaN or cleared)
+    both = torch.isfinite(pool_p) | torch.isfinite(pool_f)
+    assert torch.equal(torch.isfinite(pool_p), torch.isfinite(pool_f))
+    assert torch.equal(pool_p[both], pool_f[both])
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_block_part_wires_norms_mixer_and_feed_forward(rts, dtype):
     rt = rts[dtype]
