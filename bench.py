@@ -548,7 +548,9 @@ def main() -> int:
                    "peaks": pk_src, "device": torch.cuda.get_device_name(0),
                    "gate": "tiny model against the plain implementation: passed"},
         "e2e": {"value": round(e2e_tokens / e2e_s, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 * args.batch},
+                "h2d_bytes_per_step": int(h2d),
+                # the sampled tokens and the kernels' status word
+                "d2h_bytes_per_step": 4 * args.batch + 4},
         "gpu_launches": int(launches),
         "library_gemm_launches": int(getattr(ops, "library_launches", 0)),
         "prefill": prefill,
