@@ -338,8 +338,11 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=MODEL["max_seq_len"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--shape", default="8b", choices=["8b", "1b", "7b"],
+                    help="layer sizes of the decode line: Llama-3-8B (the contract's), "
+                         "Llama-3.2-1B or Llama-2-7B shape")
+    ap.add_argument("--context", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-serving", action="store_true",
                     help="skip the short serving workloads of points.served_*")
@@ -378,7 +381,13 @@ def main() -> int:
     from mini_llm_stack_b200.engine.runner import random_model
 
     pk, pk_src = peaks()
-    raw = dict(MODEL, n_layers=args.layers)
+    shape = {"8b": MODEL, "1b": MODEL_1B, "7b": MODEL_7B}[args.shape]
+    full_layers = shape["n_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    if args.context is None:
+        args.context = shape["max_seq_len"]
+    raw = dict(shape, n_layers=args.layers)
     cfg = config_from_dict(raw)
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
@@ -532,14 +541,17 @@ def main() -> int:
             points[key + "_preemptions"] = w["preemptions"]
 
     line = {
-        "metric": "decode tok/s at batch 8, Llama-3-8B shape, context 8192 "
+        "metric": f"decode tok/s at batch {args.batch}, "
+                  f"{ {'8b': 'Llama-3-8B', '1b': 'Llama-3.2-1B', '7b': 'Llama-2-7B'}[args.shape]} "
+                  f"shape, context {ctx} "
                   "(batch 1/64 in points; prefill tok/s at 2,048 tokens in prefill)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "llama-3-8b-shape", "layers": args.layers,
-                   "layers_of_config": FULL_LAYERS, "hidden": raw["d_model"],
+        "config": {"model": {"8b": "llama-3-8b-shape", "1b": "llama-3.2-1b-shape",
+                             "7b": "llama-2-7b-shape"}[args.shape], "layers": args.layers,
+                   "layers_of_config": full_layers, "hidden": raw["d_model"],
                    "heads": raw["n_heads"], "kv_heads": raw["n_kv_heads"],
                    "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
                    "vocab": raw["vocab_size"], "global_batch": args.batch, "seq_len": ctx,
