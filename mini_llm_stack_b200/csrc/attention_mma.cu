@@ -50,6 +50,8 @@ struct Params {
     float* part_lse;                     // [splits, T * H]       (log2 domain)
     int max_blocks, n_req, n_tokens, n_heads, n_kv, group, block_size, window, n_split;
     int small_only;                      // tile kernel: 1 = skip requests the split kernel takes
+    int cluster_merge;                   // split TMA kernel: the splits of a request and kv head are
+                                         // one cluster and merge through shared memory
     float scale_log2;                    // scale * log2(e)
     int* status;                         // device status word (a bounded wait that ran out)
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
@@ -721,6 +723,10 @@ attention_split_tma_kernel(const Params P, const Fused F,
         chain_wait();
         produce_tiles(P, &kmap, &vmap, &kmap_wide, &vmap_wide, table, kvh, kb_first, ahead,
                       n_tiles, lo, hi, base, bar0, /*late_slot=*/-1);
+        if (P.cluster_merge) {           // every thread of the cluster meets at its two barriers
+            cluster_sync_all();
+            cluster_sync_all();
+        }
         return;
     }
     chain_wait();
@@ -994,12 +1000,56 @@ attention_split_tma_kernel(const Params P, const Fused F,
         const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
         if (P.n_split == 1) {
             P.out[unit * HD + d] = __float2bfloat16_rn(val);
+        } else if (P.cluster_merge) {
+            // this CTA's result stays in its shared memory for the merge inside the cluster
+            o_s[(size_t)4 * 16 * HD + idx] = val;
+            if (d == 0) o_s[(size_t)5 * 16 * HD + row] = l > 0.f ? m + log2f(l) : -INFINITY;
         } else {
             const size_t units = (size_t)P.n_tokens * P.n_heads;
             P.part_o[((size_t)split * units + unit) * HD + d] = val;
             if (d == 0)
                 P.part_lse[(size_t)split * units + unit] = l > 0.f ? m + log2f(l) : -INFINITY;
         }
+    }
+    if (P.cluster_merge) {
+        // The CTAs of this request and kv head (one per stretch of the context) are one
+        // cluster: each merges a share of the (row, element) pairs, reading every CTA's
+        // result and log-sum from its shared memory; weights 2^(lse - max lse), normalised,
+        // added in the order of the stretches.
+        cluster_sync_all();
+        const uint32_t cta_o = smem_u32(o_s + (size_t)4 * 16 * HD);
+        const uint32_t cta_lse = smem_u32(o_s + (size_t)5 * 16 * HD);
+        auto peer = [](uint32_t addr, int rank) {
+            uint32_t ra;
+            float v;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(addr), "r"(rank));
+            asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(ra) : "memory");
+            return v;
+        };
+        for (int idx = split * 128 + threadIdx.x; idx < rows * HD; idx += P.n_split * 128) {
+            const int row = idx / HD, d = idx - row * HD;
+            float lse[8], m = -INFINITY;
+#pragma unroll
+            for (int sidx = 0; sidx < 8; ++sidx) {
+                lse[sidx] = sidx < P.n_split ? peer(cta_lse + row * 4, sidx) : -INFINITY;
+                m = fmaxf(m, lse[sidx]);
+            }
+            float wsum = 0.f, acc = 0.f;
+            if (m != -INFINITY) {
+#pragma unroll
+                for (int sidx = 0; sidx < 8; ++sidx) {
+                    if (sidx < P.n_split) {
+                        const float w = fast_exp2(lse[sidx] - m);
+                        wsum += w;
+                        acc += w * peer(cta_o + idx * 4, sidx);
+                    }
+                }
+            }
+            const int i = row / P.group, g = row - i * P.group;
+            const size_t unit = (size_t)(tok0 + i) * P.n_heads + (kvh * P.group + g);
+            P.out[unit * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+        }
+        cluster_sync_all();              // nobody's shared memory goes away while it is read
     }
 }
 
@@ -1229,7 +1279,7 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
 constexpr int TILE_TMA_SMEM = TSTAGES * KV_STAGE + 16 * TSTAGES + 1024;
 
 constexpr int TMA_SMEM_PIPE = TSTAGES * KV_STAGE + 16 * ROWB + 16 * TSTAGES + 1024;
-constexpr int TMA_SMEM_MERGE = (128 + 4 * 16 * HD) * 4 + 1024;
+constexpr int TMA_SMEM_MERGE = (128 + 6 * 16 * HD) * 4 + 1024;   // + this CTA's result and log-sums
 constexpr int TMA_SMEM = TMA_SMEM_PIPE > TMA_SMEM_MERGE ? TMA_SMEM_PIPE : TMA_SMEM_MERGE;
 
 // Tensor maps of the pools, made once per (pool, size) and kept.
@@ -1256,6 +1306,36 @@ static bool pool_map(const void* pool, long long pool_rows, int block, CUtensorM
     }
     *out = it->second;
     return true;
+}
+
+// The split kernel and what merges its context splits: two to eight splits are launched as
+// clusters (one per request and kv head) that merge through their shared memory, if all CTAs
+// are resident at once (with several rounds of CTAs, having to place whole clusters costs
+// more than the merge kernel: 2.5 % of a step at batch 64); otherwise the splits leave their
+// results in scratch memory for attention_merge_kernel.
+// MLS_B200_CLUSTER_MERGE=0 keeps the merge kernel for every count.
+static int launch_split_tma(Params P, const Fused& F, const CUtensorMap& kmap,
+                            const CUtensorMap& vmap, const CUtensorMap& kmap_wide,
+                            const CUtensorMap& vmap_wide, int merge_tokens, cudaStream_t stream) {
+    static const bool allowed = [] {
+        const char* v = getenv("MLS_B200_CLUSTER_MERGE");
+        return !(v && v[0] == '0');
+    }();
+    const dim3 grid(P.n_req, P.n_kv, P.n_split);
+    P.cluster_merge = (allowed && P.n_split >= 2 && P.n_split <= 8 &&
+                       (long long)P.n_req * P.n_kv * P.n_split <= 2LL * sm_count()) ? 1 : 0;
+    if (P.cluster_merge) {
+        const int rc = launch_chained_cluster(attention_split_tma_kernel, grid, dim3(TMA_THREADS),
+                                              TMA_SMEM, stream, dim3(1, 1, P.n_split), P, F, kmap,
+                                              vmap, kmap_wide, vmap_wide);
+        return rc ? rc : launch_status();
+    }
+    MLS_LAUNCH((attention_split_tma_kernel), grid, dim3(TMA_THREADS), TMA_SMEM, stream, P, F, kmap,
+               vmap, kmap_wide, vmap_wide);
+    if (P.n_split > 1)
+        MLS_LAUNCH((attention_merge_kernel), dim3(merge_tokens, P.n_heads),
+                   dim3(HD < 32 ? 32 : (HD < 128 ? HD : 128)), 0, stream, P);
+    return launch_status();
 }
 #endif  // MLS_HEAD_DIM % 64 == 0
 
@@ -1308,6 +1388,7 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     P.window = window;
     P.n_split = n_split;
     P.small_only = n_small ? 1 : 0;
+    P.cluster_merge = 0;
     P.scale_log2 = scale * LOG2E;
     P.status = status;
     P.n_pages = pool_pages;
@@ -1350,12 +1431,10 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     if (n_small) {
 #if MLS_HEAD_DIM % 64 == 0
         if (tma_ok)
-            MLS_LAUNCH((attention_split_tma_kernel), dim3(n_req, n_kv, n_split), dim3(TMA_THREADS),
-                       TMA_SMEM, stream, P, Fused{}, kmap, vmap, kmap_wide, vmap_wide);
-        else
+            return launch_split_tma(P, Fused{}, kmap, vmap, kmap_wide, vmap_wide, n_tokens, stream);
 #endif
-            MLS_LAUNCH((attention_split_kernel), dim3(n_req, n_kv, n_split), dim3(NT), SPLIT_SMEM,
-                       stream, P);
+        MLS_LAUNCH((attention_split_kernel), dim3(n_req, n_kv, n_split), dim3(NT), SPLIT_SMEM,
+                   stream, P);
         int rc = launch_status();
         if (rc) return rc;
         if (n_split > 1) {
@@ -1424,6 +1503,7 @@ MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long lon
     P.window = window;
     P.n_split = n_split;
     P.small_only = 1;
+    P.cluster_merge = 0;
     P.scale_log2 = scale * LOG2E;
     P.status = status;
     P.n_pages = pool_pages;
@@ -1439,12 +1519,7 @@ MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long lon
     F.v_out = (__nv_bfloat16*)v_pool;
     F.max_pos = max_pos;
     F.writes = writes ? 1 : 0;
-    MLS_LAUNCH((attention_split_tma_kernel), dim3(n_req, n_kv, n_split), dim3(TMA_THREADS), TMA_SMEM,
-               stream, P, F, kmap, vmap, kmap_wide, vmap_wide);
-    if (n_split > 1)
-        MLS_LAUNCH((attention_merge_kernel), dim3(n_req, n_heads),
-                   dim3(HD < 32 ? 32 : (HD < 128 ? HD : 128)), 0, stream, P);
-    return launch_status();
+    return launch_split_tma(P, F, kmap, vmap, kmap_wide, vmap_wide, n_req, stream);
 #else
     return MLS_ERR_UNSUPPORTED;
 #endif

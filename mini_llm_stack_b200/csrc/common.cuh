@@ -221,6 +221,29 @@ static inline int launch_chained(void (*kernel)(Params...), dim3 grid, dim3 bloc
     return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
 
+// The same for a kernel whose CTAs form clusters of (cx, cy, cz) (the grid must be a multiple
+// of the cluster in every dimension).
+template <typename... Params, typename... Args>
+static inline int launch_chained_cluster(void (*kernel)(Params...), dim3 grid, dim3 block,
+                                         size_t smem, cudaStream_t stream, dim3 cluster,
+                                         Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster.x;
+    attr[0].val.clusterDim.y = cluster.y;
+    attr[0].val.clusterDim.z = cluster.z;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = chained_launches() ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // Launch inside a launcher that returns an int: leaves with the error if there is one.
 #define MLS_LAUNCH(kernel, grid, block, smem, stream, ...)                              \
     do {                                                                                \

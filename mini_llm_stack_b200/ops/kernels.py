@@ -479,7 +479,10 @@ class Ops:
                 scratch = self.scratch("attention_partials", n_split * units * (hd + 1))
                 part_o = scratch[:n_split * units * hd]
                 part_lse = scratch[n_split * units * hd:]
-            self.launches += (1 if n_tiles else 0) + (n_small and (2 if n_split > 1 else 1))
+            tma = (self.attention_impl != "no_tma" and hd % 64 == 0
+                   and g.block_size in (8, 16, 32, 64))
+            self.launches += (1 if n_tiles else 0) + (n_small and self._split_launches(
+                n_split, tma, step.n_requests * n_kv * n_split))
             _check(fn(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
                       _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                       step.n_requests, t, n_heads, n_kv, g.block_size, float(scale), int(window),
@@ -494,6 +497,16 @@ class Ops:
             _ptr(g.block_table), g.max_blocks, _ptr(step.positions), _ptr(step.req_of_token),
             t, n_heads, n_kv, hd, g.block_size, float(scale), int(window),
             cache.k_pool.shape[1], self._stream()), "attention_simt")
+
+    def _split_launches(self, n_split: int, tma: bool, n_ctas: int) -> int:
+        """Kernels the context-split attention launches: two to eight splits merge inside
+        clusters of the one kernel if all its CTAs are resident at once, else through a
+        merge kernel."""
+        if n_split == 1:
+            return 1
+        in_clusters = (tma and n_split <= 8 and n_ctas <= 2 * self.sm_count
+                       and os.environ.get("MLS_B200_CLUSTER_MERGE", "1") != "0")
+        return 1 if in_clusters else 2
 
     def can_fuse_rope_attention(self, hd: int, block_size: int) -> bool:
         """Whether a step of single decoded tokens can leave the rotation and the cache
@@ -528,7 +541,7 @@ class Ops:
             scratch = self.scratch("attention_partials", n_split * units * (hd + 1))
             part_o = scratch[:n_split * units * hd]
             part_lse = scratch[n_split * units * hd:]
-        self.launches += 2 if n_split > 1 else 1
+        self.launches += self._split_launches(n_split, True, step.n_requests * n_kv * n_split)
         _check(fn(parts.parts.data_ptr(), parts.parts.shape[0], t * width, _ptr(step.positions),
                   _ptr(cos), _ptr(sin), max_pos, _ptr(g.slot_map), 1 if cache.writes else 0,
                   _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool), _ptr(g.block_table),
