@@ -396,7 +396,9 @@ def main() -> int:
     ctx = min(args.context, cfg.max_seq_len)
     max_b = max(args.batch, 1 if args.no_points else 64)
     pages_per_req = (ctx + PAGE - 1) // PAGE
-    engine = Engine(model, num_blocks=max_b * pages_per_req + 8, block_size=PAGE,
+    # room for every decoding request at its full context, and for the prompt of the prefill line
+    engine = Engine(model, num_blocks=max(max_b * pages_per_req, PREFILL_TOKENS // PAGE) + 8,
+                    block_size=PAGE,
                     max_batch=max_b, max_tokens_per_step=max(PREFILL_TOKENS, max_b),
                     chunk_size=PREFILL_TOKENS)
     runner, cache = engine.runner, engine.cache

@@ -583,6 +583,7 @@ constexpr int HALF_BYTES = BN * 128;                    // 64 keys x 128 bytes
 constexpr int KV_STAGE = 2 * HALVES * HALF_BYTES;       // keys, then values
 constexpr int TSTAGES = HD <= 128 ? 3 : 2;
 constexpr int TMA_THREADS = 160;                        // 4 consumer warps + 1 producer warp
+constexpr int MAX_CLUSTER = 8;                          // most context splits merged inside a cluster
 
 // address of the 16-byte chunk `chunk` (of the whole head) of key row `row`
 __device__ __forceinline__ uint32_t swz(uint32_t tile, int row, int chunk) {
@@ -1028,16 +1029,16 @@ attention_split_tma_kernel(const Params P, const Fused F,
         };
         for (int idx = split * 128 + threadIdx.x; idx < rows * HD; idx += P.n_split * 128) {
             const int row = idx / HD, d = idx - row * HD;
-            float lse[8], m = -INFINITY;
+            float lse[MAX_CLUSTER], m = -INFINITY;
 #pragma unroll
-            for (int sidx = 0; sidx < 8; ++sidx) {
+            for (int sidx = 0; sidx < MAX_CLUSTER; ++sidx) {
                 lse[sidx] = sidx < P.n_split ? peer(cta_lse + row * 4, sidx) : -INFINITY;
                 m = fmaxf(m, lse[sidx]);
             }
             float wsum = 0.f, acc = 0.f;
             if (m != -INFINITY) {
 #pragma unroll
-                for (int sidx = 0; sidx < 8; ++sidx) {
+                for (int sidx = 0; sidx < MAX_CLUSTER; ++sidx) {
                     if (sidx < P.n_split) {
                         const float w = fast_exp2(lse[sidx] - m);
                         wsum += w;
@@ -1311,8 +1312,9 @@ static bool pool_map(const void* pool, long long pool_rows, int block, CUtensorM
 // The split kernel and what merges its context splits: two to eight splits are launched as
 // clusters (one per request and kv head) that merge through their shared memory, if all CTAs
 // are resident at once (with several rounds of CTAs, having to place whole clusters costs
-// more than the merge kernel: 2.5 % of a step at batch 64); otherwise the splits leave their
-// results in scratch memory for attention_merge_kernel.
+// more than the merge kernel: 2.5 % of a step at batch 64; and sixteen splits in clusters of
+// sixteen lost 2 % at batch 1 against twenty-two splits and the merge kernel); otherwise the
+// splits leave their results in scratch memory for attention_merge_kernel.
 // MLS_B200_CLUSTER_MERGE=0 keeps the merge kernel for every count.
 static int launch_split_tma(Params P, const Fused& F, const CUtensorMap& kmap,
                             const CUtensorMap& vmap, const CUtensorMap& kmap_wide,
@@ -1322,7 +1324,7 @@ static int launch_split_tma(Params P, const Fused& F, const CUtensorMap& kmap,
         return !(v && v[0] == '0');
     }();
     const dim3 grid(P.n_req, P.n_kv, P.n_split);
-    P.cluster_merge = (allowed && P.n_split >= 2 && P.n_split <= 8 &&
+    P.cluster_merge = (allowed && P.n_split >= 2 && P.n_split <= MAX_CLUSTER &&
                        (long long)P.n_req * P.n_kv * P.n_split <= 2LL * sm_count()) ? 1 : 0;
     if (P.cluster_merge) {
         const int rc = launch_chained_cluster(attention_split_tma_kernel, grid, dim3(TMA_THREADS),

@@ -29,14 +29,17 @@ class AttentionPlan:
     n_split: int          # parts the context of the small requests is cut into
 
 
-def context_splits(n_small: int, longest: int, n_kv: int, slots: int = 296) -> int:
+def context_splits(n_small: int, longest: int, n_kv: int, slots: int = 296,
+                   cluster_splits: int = 0) -> int:
     """Context splits for ``n_small`` decoding requests of up to ``longest`` keys.
 
     ``slots`` CTAs of the split kernel run at a time (two an SM: 296 on a B200); the cost
     of a choice is its number of such waves times the 64-key tiles a CTA walks (plus six
     tiles' worth of start-up), plus the merge kernel's time, which grows with the number
-    of parts (measured at batch 1: 16 parts beat 32).  The cheapest choice wins; a split
-    is never shorter than 256 keys.
+    of parts (measured at batch 1: 16 parts beat 32).  Up to ``cluster_splits`` parts are
+    merged inside the split kernel while one round of CTAs holds them all; beyond that a
+    merge kernel follows, which costs about what two tiles take.  The cheapest choice
+    wins; a split is never shorter than 256 keys.
     """
     forced = os.environ.get("MLS_B200_SPLITS")
     if forced:
@@ -47,6 +50,8 @@ def context_splits(n_small: int, longest: int, n_kv: int, slots: int = 296) -> i
     for s in range(1, max(1, min(64, longest // 256)) + 1):
         waves = -(-pairs * s // slots)
         cost = waves * (-(-tiles // s) + 6) + (0.3 * s if s > 1 else 0.0)
+        if s > 1 and cluster_splits and not (s <= cluster_splits and pairs * s <= slots):
+            cost += 2.0
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
@@ -112,7 +117,8 @@ class GroupedQueryAttention(Mixer):
             n_split = 1
             if n_small:
                 longest = max(c for c, s in zip(step.ctx_lens, small) if s)
-                n_split = context_splits(n_small, longest, self.n_kv_heads, f["split_slots"])
+                n_split = context_splits(n_small, longest, self.n_kv_heads, f["split_slots"],
+                                         f.get("cluster_splits", 0))
             plan = AttentionPlan(
                 n_tiles=sum(-(-r // f["tile_rows"]) for r in big),
                 n_tiles_tc=sum(-(-r // f["tc_rows"]) for r in big),
