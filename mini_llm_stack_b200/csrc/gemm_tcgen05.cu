@@ -44,7 +44,25 @@ struct GemmParams {
     int splits;                          // parts along K
     int epilogue;                        // 0: store D; 1: SwiGLU over interleaved gate / up blocks of 16
     int* status;
+    // pairs of CTAs only: the tiles from tail_full on are cut along K into tail_parts parts of
+    // tail_per k-blocks, whose raw sums go to `partial` (tail_parts <= 1: no tile is cut)
+    int tail_full = 0, tail_parts = 0, tail_per = 0;
 };
+
+// The tiles of a product on pairs of CTAs are dealt out in rounds of one tile a pair.  The
+// tiles that would make a last, incomplete round (those from tail_full on) are cut along K so
+// that every pair gets a piece, and the pieces come first: their sums are stored while the
+// first whole tiles are multiplied.  Unit u < cut is part u % tail_parts of tile
+// tail_full + u / tail_parts; the later units are the whole tiles 0 .. tail_full - 1.
+struct PairUnit {
+    int tile, kb0, kb1, part;            // part < 0: a whole tile
+};
+__device__ __forceinline__ PairUnit pair_unit(const GemmParams& p, int u, int cut, int kblocks) {
+    if (u >= cut) return {u - cut, 0, kblocks, -1};
+    const int t = u / p.tail_parts, part = u - t * p.tail_parts;
+    const int kb0 = part * p.tail_per;
+    return {p.tail_full + t, kb0, min(kblocks, kb0 + p.tail_per), part};
+}
 
 template <int BN, int STAGES>
 struct Smem {
@@ -370,7 +388,8 @@ template <int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
 gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap amap,
                          const __grid_constant__ CUtensorMap bmap,
-                         const __grid_constant__ CUtensorMap omap, int staged_stores) {
+                         const __grid_constant__ CUtensorMap omap,
+                         const __grid_constant__ CUtensorMap pmap, int staged_stores) {
     using L = PairSmem<STAGES>;
     constexpr int BN = PAIR_BN;
     constexpr int TMEM_COLS = 2 * BN;                        // two accumulators of 256 columns
@@ -390,6 +409,8 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
     const int tile_count = m_pairs * n_tiles;
     const int kblocks = (p.k + BK - 1) / BK;
     const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+    const int cut = p.tail_parts > 1 ? (tile_count - p.tail_full) * p.tail_parts : 0;
+    const int unit_count = cut ? cut + p.tail_full : tile_count;
 
     chain_release();
     if (threadIdx.x == 0) {
@@ -415,10 +436,11 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         // ------------------------------------------------------------- TMA producer
         if (lane == 0) {
             int g = 0;
-            for (int tile = cluster; tile < tile_count && !timed_out; tile += clusters) {
-                const int mi = tile % m_pairs, ni = tile / m_pairs;
+            for (int unit = cluster; unit < unit_count && !timed_out; unit += clusters) {
+                const PairUnit w = pair_unit(p, unit, cut, kblocks);
+                const int mi = w.tile % m_pairs, ni = w.tile / m_pairs;
                 const int a_row = mi * 2 * BM + (int)rank * BM, b_row = ni * BN + (int)rank * BM;
-                for (int i = 0; i < kblocks; ++i, ++g) {
+                for (int i = w.kb0; i < w.kb1; ++i, ++g) {
                     const int slot = g % STAGES;
                     if (!mbar_wait(empty(slot), ((g / STAGES) & 1) ^ 1)) {
                         timed_out = true;
@@ -442,7 +464,8 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             // ----------------------------------------------- MMA issue for the pair
             constexpr uint32_t idesc = umma_idesc_pair(BN);
             int g = 0, it = 0;
-            for (int tile = cluster; tile < tile_count && !timed_out; tile += clusters, ++it) {
+            for (int unit = cluster; unit < unit_count && !timed_out; unit += clusters, ++it) {
+                const PairUnit w = pair_unit(p, unit, cut, kblocks);
                 const int acc = it & 1;
                 if (!mbar_wait_cluster(acc_empty(acc), ((it >> 1) & 1) ^ 1)) {
                     timed_out = true;
@@ -450,7 +473,7 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int i = 0; i < kblocks; ++i, ++g) {
+                for (int i = w.kb0; i < w.kb1; ++i, ++g) {
                     const int slot = g % STAGES;
                     if (!mbar_wait_cluster(full(slot), (g / STAGES) & 1)) {
                         timed_out = true;
@@ -461,7 +484,8 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk)
                         umma_pair(tmem_d, umma_desc(a_src + kk * UMMA_K * 2),
-                                  umma_desc(b_src + kk * UMMA_K * 2), idesc, (i | kk) ? 1u : 0u);
+                                  umma_desc(b_src + kk * UMMA_K * 2), idesc,
+                                  (i > w.kb0 || kk) ? 1u : 0u);
                     umma_commit_pair(empty(slot), 3);        // both CTAs' stage is free
                 }
                 umma_commit_pair(acc_full(acc), 3);          // both CTAs' accumulator is complete
@@ -474,8 +498,9 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
         const bool issuer = q == 0 && lane == 0;
         const int acc_cols = p.epilogue == 1 ? 128 : 64;     // accumulator columns behind 64 outputs
         int it = 0, fills = 0;
-        for (int tile = cluster; tile < tile_count; tile += clusters, ++it) {
-            const int mi = tile % m_pairs, ni = tile / m_pairs;
+        for (int unit = cluster; unit < unit_count; unit += clusters, ++it) {
+            const PairUnit w = pair_unit(p, unit, cut, kblocks);
+            const int mi = w.tile % m_pairs, ni = w.tile / m_pairs;
             const int acc = it & 1;
             const int row0 = mi * 2 * BM + (int)rank * BM;
             const int row = row0 + row_in;
@@ -485,6 +510,46 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
             }
             tc_fence_after();
             const uint32_t tmem_d = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+            if (w.part >= 0) {
+                // a part of a cut tile: the raw sums, [tile of the tail][part][256 rows][256],
+                // 32 columns at a time through the staging tiles (128 bytes a row)
+                const int part_row0 =
+                    ((w.tile - p.tail_full) * p.tail_parts + w.part) * (2 * BM) + (int)rank * BM;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32, ++fills) {
+                    const uint32_t stage = base + L::OUT + (fills & 1) * L::OUT_TILE;
+                    if (issuer) tma_store_wait_read<1>();
+                    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                    uint32_t ra[16], rb[16];
+                    tmem_ld16(tmem_d + c0, ra);
+                    tmem_ld16(tmem_d + c0 + 16, rb);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
+                                     ::"r"(stage + row_in * 128 + ((ch ^ (row_in & 7)) << 4)),
+                                       "r"(ra[4 * ch]), "r"(ra[4 * ch + 1]), "r"(ra[4 * ch + 2]),
+                                       "r"(ra[4 * ch + 3]) : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
+                                     ::"r"(stage + row_in * 128 + (((ch + 4) ^ (row_in & 7)) << 4)),
+                                       "r"(rb[4 * ch]), "r"(rb[4 * ch + 1]), "r"(rb[4 * ch + 2]),
+                                       "r"(rb[4 * ch + 3]) : "memory");
+                    }
+                    if (c0 + 32 >= BN) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (rank == 0) mbar_arrive(acc_empty(acc));
+                            else mbar_arrive_remote(acc_empty(acc), 0);
+                        }
+                    }
+                    fence_proxy_async();
+                    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                    // the map sees the float32 scratch as rows of 512 two-byte elements
+                    if (issuer) tma_store_2d(&pmap, c0 * 2, part_row0, stage);
+                }
+                continue;
+            }
             if (staged_stores) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += acc_cols, ++fills) {
@@ -618,6 +683,45 @@ __global__ void splitk_sum_kernel(const float* __restrict__ partial, void* __res
     }
 }
 
+// The cut tiles of a product on pairs of CTAs: their parts added up in the order of the
+// parts, then the epilogue.  One thread an output; the loads of eight parts are under way
+// at a time.
+__global__ void pair_tail_sum_kernel(const GemmParams p, int m_pairs, int tail_tiles) {
+    chain_release();
+    chain_wait();
+    constexpr int TILE = 2 * BM, BN = 256;
+    const int shift = p.epilogue == 1 ? 7 : 8, outs = 1 << shift;   // outputs of a tile's row
+    const int width = p.epilogue == 1 ? p.nn / 2 : p.nn;
+    const unsigned total = (unsigned)tail_tiles * TILE * outs;
+    const size_t part_stride = (size_t)TILE * BN;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int o = (int)(i & (outs - 1)), r = (int)((i >> shift) & (TILE - 1)),
+                  t = (int)(i >> (shift + 8));
+        const int tile = p.tail_full + t, mi = tile % m_pairs, ni = tile / m_pairs;
+        const int row = mi * TILE + r, col = ni * outs + o;
+        if (row >= p.mm || col >= width) continue;
+        const float* src = p.partial + ((size_t)t * p.tail_parts * TILE + r) * BN;
+        float v;
+        if (p.epilogue == 1) {
+            const int g = (o / 16) * 32 + (o % 16);
+            float gs = 0.f, us = 0.f;
+#pragma unroll 8
+            for (int k = 0; k < p.tail_parts; ++k) {
+                gs += src[k * part_stride + g];
+                us += src[k * part_stride + g + 16];
+            }
+            v = silu_mul(gs, us);
+        } else {
+            v = 0.f;
+#pragma unroll 8
+            for (int k = 0; k < p.tail_parts; ++k) v += src[k * part_stride + o];
+        }
+        const size_t at = (size_t)row * p.ld_out + col;
+        if (p.out_f32) ((float*)p.out)[at] = v;
+        else ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(v);
+    }
+}
+
 struct MapKey {
     const void* ptr;
     long long rows, k;
@@ -682,6 +786,49 @@ int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
     return launch_status();
 }
 
+// How a product on pairs of CTAs cuts the tiles of its last round (see pair_unit): so many
+// parts that every pair gets one, at least four k-blocks each.  parts <= 1: nothing is cut.
+// How a product on pairs of CTAs cuts the tiles of its last round (see pair_unit): so many
+// parts that every pair gets one, at least four k-blocks each.  parts <= 1: nothing is cut.
+//
+// When it pays (measured, Llama-3-8B products): at full occupancy the pairs are bound by what
+// all SMs together draw from L2, not by rounds, so a last round of a few tiles runs faster
+// than a whole one and cutting it only moves work; the parts cost a float32 round trip
+// through L2 and a second kernel.  512 x 28,672 x 4,096 with SwiGLU (three rounds and two
+// tiles): 99.5 us cut, 106.8 whole; 2,048 rows of the same (twelve rounds and eight tiles):
+// 326.6 against 322.7; 512 x 4,096 x 14,336 (32 tiles in all): 59 against 81; 512 x 4,096 x
+// 4,096: 30.4 against 29.1.  So: cut a last round of at most a sixteenth of the pairs, or a
+// single incomplete round whose K is long (128 k-blocks or more).
+// MLS_B200_GEMM_TAIL = 0 never cuts, "always" cuts whenever every piece gets four k-blocks.
+int g_cut_tail = [] {
+    const char* v = getenv("MLS_B200_GEMM_TAIL");
+    if (v && v[0] == '0') return 0;
+    return (v && v[0] == 'a') ? 2 : 1;
+}();
+
+struct TailPlan {
+    int full, parts, per;
+    long long floats;                    // float32 scratch for the parts
+};
+TailPlan tail_plan(int m, int n, int k) {
+    TailPlan t{0, 0, 0, 0};
+    const long long tiles = (long long)((m + 2 * BM - 1) / (2 * BM)) * ((n + PAIR_BN - 1) / PAIR_BN);
+    const int most = sm_count() / 2, kblocks = (k + BK - 1) / BK;
+    if (!g_cut_tail || most <= 0) return t;
+    const int tail = (int)(tiles % most);
+    if (tail == 0) return t;
+    const bool pays = tail * 16 <= most || (tiles < most && kblocks >= 128);
+    if (g_cut_tail == 1 && !pays) return t;
+    int parts = most / tail;
+    if (parts > kblocks / 4) parts = kblocks / 4;
+    if (parts < 2) return t;
+    t.per = (kblocks + parts - 1) / parts;
+    t.parts = (kblocks + t.per - 1) / t.per;
+    t.full = (int)(tiles - tail);
+    t.floats = (long long)tail * t.parts * (2 * BM) * PAIR_BN;
+    return t;
+}
+
 template <int STAGES>
 int launch_pair(const GemmParams& p, const void* a, const void* b, cudaStream_t stream) {
     using L = PairSmem<STAGES>;
@@ -704,12 +851,34 @@ int launch_pair(const GemmParams& p, const void* a, const void* b, cudaStream_t 
     } else {
         omap = amap;                                         // unused
     }
-    const long long tiles = (long long)((p.mm + 2 * BM - 1) / (2 * BM)) *
-                            ((p.nn + PAIR_BN - 1) / PAIR_BN);
+    GemmParams q = p;
+    CUtensorMap pmap = amap;                                 // unused unless tiles are cut
+    const TailPlan plan = tail_plan(p.mm, p.nn, p.k);
+    const int m_pairs = (p.mm + 2 * BM - 1) / (2 * BM);
+    const long long tiles = (long long)m_pairs * ((p.nn + PAIR_BN - 1) / PAIR_BN);
+    long long units = tiles;
+    if (plan.parts > 1 && p.partial != nullptr && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0) {
+        // the scratch as [pieces x 256 rows] of 256 float32 = 512 two-byte elements, in boxes of
+        // 128 rows x 128 bytes
+        const long long rows = (tiles - plan.full) * plan.parts * 2 * BM;
+        if (!output_map(p.partial, rows, 2 * PAIR_BN, 2 * PAIR_BN, &pmap)) return MLS_ERR_TENSOR_MAP;
+        q.tail_full = plan.full;
+        q.tail_parts = plan.parts;
+        q.tail_per = plan.per;
+        units = plan.full + (tiles - plan.full) * plan.parts;
+    }
     const long long most = sm_count() / 2;                   // one pair on two SMs
-    const int grid = 2 * (int)(tiles < most ? tiles : most);
-    MLS_LAUNCH((gemm_tcgen05_pair_kernel<STAGES>), dim3(grid), dim3(THREADS), L::TOTAL, stream, p,
-               amap, bmap, omap, staged);
+    const int grid = 2 * (int)(units < most ? units : most);
+    MLS_LAUNCH((gemm_tcgen05_pair_kernel<STAGES>), dim3(grid), dim3(THREADS), L::TOTAL, stream, q,
+               amap, bmap, omap, pmap, staged);
+    int rc = launch_status();
+    if (rc || q.tail_parts <= 1) return rc;
+    const int tail_tiles = (int)(tiles - plan.full);
+    const long long work = (long long)tail_tiles * 2 * BM * (p.epilogue == 1 ? 128 : 256);
+    long long blocks = (work + 255) / 256;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+    MLS_LAUNCH((pair_tail_sum_kernel), dim3((int)blocks), dim3(256), 0, stream, q, m_pairs,
+               tail_tiles);
     return launch_status();
 }
 
@@ -727,12 +896,24 @@ int g_prompt_kernel = [] {
 // 0: prompts of more than 128 rows take one CTA a tile; 1: pairs of CTAs.
 MLS_API void mls_gemm_set_prompt_kernel(int which) { g_prompt_kernel = which ? 1 : 0; }
 
+// The last round's tiles of a product on pairs: 0 = never cut, 1 = cut where it pays,
+// 2 = cut whenever every piece gets four k-blocks.
+MLS_API void mls_gemm_set_tail_cut(int mode) { g_cut_tail = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
+
+// float32 scratch (`partial`) that a prompt's product of this size wants for the tiles of its
+// last round; 0: none.  Without the scratch the product runs all tiles whole.
+MLS_API long long mls_gemm_prompt_scratch_floats(int m, int n, int k) {
+    if (m <= BM || g_prompt_kernel != 1) return 0;
+    return tail_plan(m, n, k).floats;
+}
+
 // out[M, N] = act[M, K] * w[N, K]^T, bfloat16 operands, out bfloat16 or float32.
 // swap: 1 = the weights take the 128-row side (decoding, M <= 64).  splits > 1 cuts K
 // (weight-major orientation only) and needs `partial`, float32 scratch of
 // splits * M * N, which a second kernel adds up (with out == nullptr the parts are left
-// to the caller, [part][M][N]).  epilogue 1: the weight rows alternate between
-// 16 gate rows and the 16 matching up rows, and out[M, N / 2] = silu(gate) * up.
+// to the caller, [part][M][N]).  With swap = 0 `partial` is optional scratch of
+// mls_gemm_prompt_scratch_floats(m, n, k) floats.  epilogue 1: the weight rows alternate
+// between 16 gate rows and the 16 matching up rows, and out[M, N / 2] = silu(gate) * up.
 MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32, int m, int n,
                           int k, int swap, int splits, int epilogue, float* partial, int* status,
                           cudaStream_t stream) {
@@ -769,7 +950,7 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
                    m, n, splits, epilogue);
         return launch_status();
     }
-    if (splits != 1) return MLS_ERR_UNSUPPORTED;               // prompts have tiles enough
+    if (splits != 1) return MLS_ERR_UNSUPPORTED;               // prompts cut K by themselves
     p.mm = m;
     p.nn = n;
     p.transposed = 0;

@@ -55,10 +55,10 @@ def _need(cond: bool, msg: str) -> None:
         raise KernelError(msg)
 
 
-def _decl(lib, name, argtypes):
+def _decl(lib, name, argtypes, restype=ctypes.c_int):
     fn = getattr(lib, name)
     fn.argtypes = argtypes
-    fn.restype = ctypes.c_int
+    fn.restype = restype
     return fn
 
 
@@ -304,15 +304,29 @@ class Ops:
         per = -(-kblocks // splits)
         return -(-kblocks // per)
 
-    def _gemm_bf16(self, a, w, out, m: int, n: int, k: int, epilogue: int = 0,
-                   leave_parts: bool = False):
-        """The tcgen05 product.  ``leave_parts``: the K-parts are not added up but
-        returned as ``SplitParts`` (the caller has checked that there are several)."""
+    def _gemm_library(self):
         if self._gemm is None:
             lib = self._load("gemm")
             self._gemm = _decl(lib, "mls_gemm_bf16",
                                [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P])
+            self._gemm_prompt_scratch = _decl(lib, "mls_gemm_prompt_scratch_floats", [_I, _I, _I],
+                                              restype=ctypes.c_longlong)
             self._gemm_lib = lib
+        return self._gemm_lib
+
+    def set_gemm_tail_cut(self, mode: str) -> None:
+        """Whether a prompt's product cuts the tiles of its last round along K: "never",
+        "auto" (where it measured faster; the default) or "always" (wherever every piece
+        gets four k-blocks)."""
+        _need(mode in ("never", "auto", "always"), f"set_gemm_tail_cut: unknown mode {mode!r}")
+        fn = _decl(self._gemm_library(), "mls_gemm_set_tail_cut", [_I], restype=None)
+        fn(("never", "auto", "always").index(mode))
+
+    def _gemm_bf16(self, a, w, out, m: int, n: int, k: int, epilogue: int = 0,
+                   leave_parts: bool = False):
+        """The tcgen05 product.  ``leave_parts``: the K-parts are not added up but
+        returned as ``SplitParts`` (the caller has checked that there are several)."""
+        self._gemm_library()
         if self.gemm_impl == "tcgen05-tiles" or self._tiles_set:
             # prompts of more than 128 rows on one CTA a tile instead of pairs of CTAs
             self._gemm_lib.mls_gemm_set_prompt_kernel.argtypes = [_I]
@@ -320,14 +334,22 @@ class Ops:
             self._tiles_set = self.gemm_impl == "tcgen05-tiles"
             self._gemm_lib.mls_gemm_set_prompt_kernel(0 if self._tiles_set else 1)
         swap = 1 if m <= 64 else 0
-        splits, partial = 1, None
+        splits, partial, sums = 1, None, 0
         if swap:
             splits = self._gemm_splits(m, n, k)
             if splits > 1:
                 tag = "gemm_kept_parts" if leave_parts else "gemm_partials"
                 partial = self.scratch(tag, splits * m * n)
+                sums = 0 if leave_parts else 1
+        else:
+            # a prompt's product cuts the tiles of its last round along K when that gives
+            # every pair of SMs a piece; a second kernel adds the pieces up
+            floats = self._gemm_prompt_scratch(m, n, k)
+            if floats:
+                partial = self.scratch("gemm_tail_parts", floats)
+                sums = 1
         _need(not leave_parts or splits > 1, "gemm_bf16: no parts to leave")
-        self.launches += 2 if splits > 1 and not leave_parts else 1
+        self.launches += 1 + sums
         out_f32 = 1 if (out is not None and out.dtype == torch.float32) else 0
         _check(self._gemm(_ptr(a), _ptr(w), None if leave_parts else _ptr(out), out_f32,
                           m, n, k, swap, splits, epilogue, _ptr(partial), _ptr(self.status),

@@ -210,7 +210,9 @@ def test_product_left_as_parts_is_summed_by_the_next_norm(rts, m, n, k):
 
 @pytest.mark.parametrize("m, inter, k", [(1, 14336, 4096), (8, 176, 64), (64, 256, 96), (33, 4096, 4096),
                                          (8, 11008, 128), (3, 10000, 64),
-                                          (300, 272, 200), (2048, 1024, 512), (129, 14336, 1024)])
+                                          (300, 272, 200), (2048, 1024, 512), (129, 14336, 1024),
+                                          # two tiles after three whole rounds, cut along K
+                                          (512, 14336, 4096)])
 def test_gate_up_projection_with_swiglu_epilogue(rts, m, inter, k):
     ops = rts[torch.bfloat16].ops
     a = rand((m, k), torch.bfloat16, 30)
@@ -223,6 +225,39 @@ def test_gate_up_projection_with_swiglu_epilogue(rts, m, inter, k):
     u = (a.float() @ wu.float().t()).cpu()
     want = torch.nn.functional.silu(g) * u
     assert (out.float().cpu() - want).abs().max().item() <= 8e-3 * want.abs().max().item() + 1e-6
+
+
+@pytest.mark.parametrize("mode", ["always", "auto"])
+@pytest.mark.parametrize("m, n, k, swiglu", [
+    (600, 1000, 4096, False),      # twelve ragged tiles, no whole round, in six parts each
+    (2500, 2048, 3080, False),     # a whole round, then six tiles in twelve parts; K ends inside a k-block
+    (2048, 512, 1024, False), (300, 96, 1000, False),
+    (512, 4096, 14336, False),     # few tiles and a long K: cut in "auto" too
+    (512, 28672, 4096, True),      # two tiles after three whole rounds: cut in "auto" too
+    (300, 2400, 512, True),        # twenty ragged tiles in halves
+    (2048, 28672, 256, True)])     # eight tiles after twelve rounds, K too short for more than one part
+def test_last_rounds_tiles_cut_along_k(rts, mode, m, n, k, swiglu):
+    """A prompt's product on pairs of CTAs whose last round of tiles is cut along K: the
+    pieces' float32 sums go through scratch and a second kernel adds them up."""
+    ops = rts[torch.bfloat16].ops
+    a, w = rand((m, k), torch.bfloat16, 41), rand((n, k), torch.bfloat16, 42, 0.05)
+    out = torch.full((m, n // 2 if swiglu else n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_impl = "tcgen05"
+    ops.set_gemm_tail_cut(mode)
+    try:
+        if swiglu:
+            ops.linear_swiglu(a, w, out)
+        else:
+            ops.linear(a, ops.prepare_weight(w), out)
+    finally:
+        ops.gemm_impl = "auto"
+        ops.set_gemm_tail_cut("auto")
+    ops.check_status()
+    want = a.float() @ w.float().t()
+    if swiglu:
+        both = want.view(m, n // 32, 2, 16)
+        want = (torch.nn.functional.silu(both[:, :, 0]) * both[:, :, 1]).reshape(m, n // 2)
+    assert (out.float() - want).abs().max().item() <= 8e-3 * want.abs().max().item() + 1e-6
 
 
 # ------------------------------------------------------------------------- swiglu
