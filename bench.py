@@ -305,8 +305,22 @@ def write_timeline(args, torch, runner, cache, ops, ctx, rand_tokens, Entry) -> 
         runner.step(e)
         runner.release("prefill")
 
+    def prefill_tail():
+        # the last portion of a prompt of four: three portions' keys are in the cache already
+        cache.admit("tail")
+        assert cache.reserve("tail", 3 * PREFILL_TOKENS)
+        cache.commit("tail", 3 * PREFILL_TOKENS)
+        e = [Entry("tail", rand_tokens(PREFILL_TOKENS), [PREFILL_TOKENS - 1])]
+        runner.reserve(e)
+        runner.step(e)
+        runner.release("tail")
+
     lines = []
-    for name, fn, warm in (("decode step", decode, 6), ("prefill step", prefill, 3)):
+    steps = [("decode step", decode, 6), ("prefill step", prefill, 3)]
+    if cache.num_blocks >= cache.pages_for(4 * PREFILL_TOKENS):
+        steps.append((f"last {PREFILL_TOKENS} tokens of a prompt of {4 * PREFILL_TOKENS}",
+                      prefill_tail, 2))
+    for name, fn, warm in steps:
         for _ in range(warm):
             fn()
         torch.cuda.synchronize()

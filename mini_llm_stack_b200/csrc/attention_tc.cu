@@ -6,18 +6,23 @@
 // scores, maxima, sums and accumulators; P rounded to bfloat16 for the second
 // product (kernels/attention_fwd.py:106).
 //
-// One CTA owns 128 rows, (token, head-in-group) pairs of one kv head, and walks the
-// keys 128 at a time (a tcgen05.mma costs about the same whatever its width, so
-// wide tiles pay):
-//   warp 0      brings keys and values in with TMA, one copy per page and 64-wide half,
-//               into a ring of two key tiles and a ring of two value tiles;
-//   warp 1      issues S = Q K^T and O += P V (tcgen05.mma), accumulators in TMEM;
-//   warps 2..9  two threads per row, each half of the tile's keys: read S from TMEM, mask,
-//               exponentiate, write P to shared memory as the next product's operand,
-//               rescale O when the running maximum has grown by more than 2^8, and
-//               store O at the end.
-// S is double-buffered in TMEM and P in shared memory, so the next tile's Q K^T and
-// this tile's P V run during the next tile's softmax.
+// A CTA runs two chains in turn.  A chain is 128 rows, (token, head-in-group) pairs of
+// one kv head, that walk key tiles of 128: S = Q K^T into tensor memory, softmax by one
+// thread a row, P written over its scores in tensor memory as bfloat16, O += P V with P
+// read from there.  While one chain's softmax runs, the tensor cores work for the other:
+//   warp 0      brings keys and values in with TMA, one copy per page and 64-wide half
+//               (one per half for a run of consecutive pages), into a ring of key tiles
+//               and a ring of value tiles;
+//   warp 1      issues the products (tcgen05.mma), accumulators in tensor memory;
+//   warps 2..5  softmax of chain 0, warps 6..9 of chain 1: read S, mask, exponentiate,
+//               write P, rescale O when the running maximum has grown by more than 2^8,
+//               and store O at the end.
+// Two ways to be two chains:
+//   two row tiles   the CTA owns 256 rows; each chain walks all key tiles of its 128 rows,
+//                   and a key tile brought in once serves both (steps with many rows);
+//   two key halves  the CTA owns 128 rows; chain 0 walks the even key tiles, chain 1 the
+//                   odd ones, and their (maximum, sum, O) are merged at the end (steps
+//                   with too few rows to fill the SMs otherwise).
 // Every wait is bounded and reports MLS_STATUS_TIMEOUT.
 #include "common.cuh"
 #include "tma.cuh"
@@ -36,35 +41,28 @@ using namespace mls_tma;
 using namespace mls_tc;
 
 constexpr int HD = MLS_HEAD_DIM;
-constexpr int CHAINS = 1;                        // row blocks of 128 a CTA owns
-constexpr int ROWS = 128 * CHAINS;               // rows of a tile
-constexpr int BN = 128;                          // keys of a tile: the wider a tcgen05.mma, the better
+constexpr int CHAIN_ROWS = 128;                  // rows of a chain
+constexpr int BN = 128;                          // keys of a tile
 constexpr int HALVES = HD / 64;
 constexpr int BLOCK = 128 * 128;                 // bytes of [128 rows][64 elements]: 16 KB
 constexpr int KBLOCK = BN * 128;                 // bytes of [128 keys][64 elements]: 16 KB
 constexpr int Q_BYTES = HALVES * BLOCK;          // per chain
-constexpr int P_BYTES = (BN / 64) * BLOCK;       // per chain and buffer: [128 rows][128 keys]
-constexpr int P_BUFS = 2;                        // the softmax writes P(j+1) while P(j) V runs
 constexpr int K_STAGE = HALVES * KBLOCK, V_STAGE = HALVES * KBLOCK;
-constexpr int K_STAGES = 2, V_STAGES = 2;
-constexpr int SOFTMAX_THREADS = 256 * CHAINS;      // two warps share 32 rows, half the keys each
+constexpr int K_STAGES = HD == 128 ? 3 : 4, V_STAGES = HD == 128 ? 2 : 4;
+constexpr int SOFTMAX_THREADS = 256;             // one thread a row, two chains
 constexpr int THREADS = 64 + SOFTMAX_THREADS;
-constexpr int TMEM_COLS = 512;                   // per chain S0 | S1, then per chain O
-constexpr int COL_S = 0, COL_O = CHAINS * 2 * BN;
-static_assert(COL_O + CHAINS * HD <= TMEM_COLS, "tensor memory columns");
+constexpr int TMEM_COLS = 512;                   // S0 | S1 | O0 | O1, 128 columns each
+constexpr int COL_S = 0, COL_O = 2 * BN;
+static_assert(COL_O + BN + HD <= TMEM_COLS, "tensor memory columns");
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;             // log2: P stays below 2^8
 
 // barrier slots
 constexpr int B_K_FULL = 0, B_K_EMPTY = K_STAGES, B_V_FULL = 2 * K_STAGES,
-              B_V_EMPTY = B_V_FULL + V_STAGES, B_S_FULL = B_V_EMPTY + V_STAGES,       // [chain][2]
-              B_S_EMPTY = B_S_FULL + 2 * CHAINS, B_P_FULL = B_S_EMPTY + 2 * CHAINS,   // [chain][buf]
-              B_P_EMPTY = B_P_FULL + P_BUFS * CHAINS, B_Q_FULL = B_P_EMPTY + P_BUFS * CHAINS,
+              B_V_EMPTY = B_V_FULL + V_STAGES, B_S_FULL = B_V_EMPTY + V_STAGES,   // [chain]
+              B_P_FULL = B_S_FULL + 2, B_O_REST = B_P_FULL + 2, B_Q_FULL = B_O_REST + 2,
               N_BARS = B_Q_FULL + 1;
-// no alignment slack: two CTAs must fit one SM; the kernel checks the alignment
-constexpr int SMEM_BYTES = CHAINS * (Q_BYTES + P_BUFS * P_BYTES) + K_STAGES * K_STAGE +
-                           V_STAGES * V_STAGE +
-                           8 * N_BARS + 16;
+constexpr int SMEM_BYTES = 2 * Q_BYTES + K_STAGES * K_STAGE + V_STAGES * V_STAGE + 8 * N_BARS + 16;
 
 struct Params {
     const __nv_bfloat16* qkv;
@@ -73,6 +71,7 @@ struct Params {
     const int* cu_q;
     const int* ctx_len;
     int max_blocks, n_req, n_heads, n_kv, group, block_size, window, small_only;
+    int two_tiles;                       // 1: a CTA owns two row tiles; 0: one, its keys in halves
     float scale_log2;
     int* status;
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
@@ -99,60 +98,79 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
     chain_release();
     chain_wait();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ float row_max[2][2][128];         // [tile parity][half of the keys][row]
+    __shared__ float2 chain_state[2][CHAIN_ROWS];    // (maximum, sum) of a row, per chain
     const uint32_t base = smem_u32(smem_raw);
     if (base & 1023u) {                          // the swizzled tiles need this alignment
         if (threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_SMEM);
         return;
     }
     uint8_t* gbase = smem_raw;
-    const uint32_t q_smem = base, p_smem = base + CHAINS * Q_BYTES,
-                   k_smem = p_smem + CHAINS * P_BUFS * P_BYTES, v_smem = k_smem + K_STAGES * K_STAGE;
+    const uint32_t q_smem = base, k_smem = base + 2 * Q_BYTES, v_smem = k_smem + K_STAGES * K_STAGE;
     const uint32_t bars = v_smem + V_STAGES * V_STAGE;
     auto bar = [&](int i) { return bars + 8u * i; };
     volatile uint32_t* tmem_slot =
         reinterpret_cast<volatile uint32_t*>(gbase + (bars - base) + 8 * N_BARS);
 
-    // which request and which 128-row tile of it; the last rows see the most keys and
+    // which request and which tile of rows of it; the last rows see the most keys and
     // go first, for all kv heads (blockIdx.x) before the next tile
+    const int tile_rows = P.two_tiles ? 2 * CHAIN_ROWS : CHAIN_ROWS;
     int r = 0, tile = blockIdx.y, q_len = 0, rows = 0;
     for (; r < P.n_req; ++r) {
         q_len = P.cu_q[r + 1] - P.cu_q[r];
         rows = q_len * P.group;
-        int tiles = (P.small_only && is_small(q_len, P.group)) ? 0 : (rows + ROWS - 1) / ROWS;
+        int tiles = (P.small_only && is_small(q_len, P.group)) ? 0 : (rows + tile_rows - 1) / tile_rows;
         if (tile < tiles) break;
         tile -= tiles;
     }
     if (r >= P.n_req) return;
-    tile = (rows + ROWS - 1) / ROWS - 1 - tile;
+    tile = (rows + tile_rows - 1) / tile_rows - 1 - tile;
     const int kvh = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok0 = P.cu_q[r], ctx = P.ctx_len[r];
-    const int row0 = tile * ROWS;
+    const int row0 = tile * tile_rows;
     const int pos0 = ctx - q_len;
     const int i_first = row0 / P.group;
-    const int i_last = (min(rows, row0 + ROWS) - 1) / P.group;
+    const int i_last = (min(rows, row0 + tile_rows) - 1) / P.group;
     const int hi = pos0 + i_last;
     const int lo = P.window > 0 ? max(0, pos0 + i_first - P.window + 1) : 0;
     const int* table = P.block_table + (size_t)r * P.max_blocks;
     const int kbase0 = (lo / BN) * BN;
     const int n_tiles = (hi - kbase0) / BN + 1;
+    // steps of each chain, and the key tile of chain c's step i
+    int n_steps[2];
+    if (P.two_tiles) {
+        // chain 0's rows end earlier: it may need a key tile less; chain 1 may have no rows
+        const int last0 = (min(rows, row0 + CHAIN_ROWS) - 1) / P.group;
+        n_steps[0] = (pos0 + last0 - kbase0) / BN + 1;
+        n_steps[1] = row0 + CHAIN_ROWS < rows ? n_tiles : 0;
+    } else {
+        n_steps[0] = (n_tiles + 1) / 2;
+        n_steps[1] = n_tiles / 2;
+    }
+    const int chains = n_steps[1] > 0 ? 2 : 1;
+    auto key_tile = [&](int c, int i) { return P.two_tiles ? i : 2 * i + c; };
 
-    // a softmax thread's half of its row of Q is asked for before the set-up below, so
-    // that the two latencies overlap
-    uint4 q_regs[HD / 16];
+    // a softmax thread's row of Q (its half of the row when both chains share the rows) is
+    // asked for before the set-up below, so that the two latencies overlap
+    const int chain = warp >= 2 ? (warp - 2) >> 2 : 0;          // of a softmax warp
+    const int quarter = warp & 3;                                // its lanes of tensor memory
+    const int row_in = quarter * 32 + lane;                      // row of the chain = TMEM lane
+    constexpr int Q_CHUNKS = HD / 8;                             // 16-byte chunks of a row
+    const int q_chunks = P.two_tiles ? Q_CHUNKS : Q_CHUNKS / 2;  // this thread's
+    const int q_chunk0 = P.two_tiles ? 0 : chain * (Q_CHUNKS / 2);
+    const int row = row0 + (P.two_tiles ? chain * CHAIN_ROWS : 0) + row_in;
+    const bool live = warp >= 2 && row < rows;
+    const int ti = live ? row / P.group : 0, g = live ? row - ti * P.group : 0;
+    uint4 q_regs[Q_CHUNKS];
     if (warp >= 2) {
-        const int q = warp & 3, half = (warp - 2) >> 2;
-        const int row = row0 + q * 32 + lane;
-        const bool live = row < rows;
-        const int ti = live ? row / P.group : 0, g = live ? row - ti * P.group : 0;
         const int row_w = (P.n_heads + 2 * P.n_kv) * HD;
         const __nv_bfloat16* src =
             P.qkv + (size_t)(tok0 + ti) * row_w + (size_t)(kvh * P.group + g) * HD;
 #pragma unroll
-        for (int i = 0; i < HD / 16; ++i) {
+        for (int i = 0; i < Q_CHUNKS; ++i) {
             q_regs[i] = make_uint4(0u, 0u, 0u, 0u);
-            if (live) q_regs[i] = *reinterpret_cast<const uint4*>(src + (half * (HD / 16) + i) * 8);
+            if (live && i < q_chunks)
+                q_regs[i] = *reinterpret_cast<const uint4*>(src + (q_chunk0 + i) * 8);
         }
     }
 
@@ -165,13 +183,10 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
             mbar_init(bar(B_V_FULL + s), 1);
             mbar_init(bar(B_V_EMPTY + s), 1);
         }
-        for (int s = 0; s < 2 * CHAINS; ++s) {
-            mbar_init(bar(B_S_FULL + s), 1);
-            mbar_init(bar(B_S_EMPTY + s), SOFTMAX_THREADS);
-        }
-        for (int c = 0; c < P_BUFS * CHAINS; ++c) {
-            mbar_init(bar(B_P_FULL + c), SOFTMAX_THREADS);
-            mbar_init(bar(B_P_EMPTY + c), 1);
+        for (int c = 0; c < 2; ++c) {
+            mbar_init(bar(B_S_FULL + c), 1);
+            mbar_init(bar(B_P_FULL + c), CHAIN_ROWS);
+            mbar_init(bar(B_O_REST + c), 1);
         }
         mbar_init(bar(B_Q_FULL), SOFTMAX_THREADS);
         fence_barrier_init();
@@ -254,121 +269,107 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(BN, 0);
             constexpr uint32_t idesc_o = umma_idesc(HD, 1);
-            // S(c, j) = Q_c K_j^T into chain c's score buffer j & 1
-            auto issue_qk = [&](int c, int j) -> bool {
-                const int slot = j % K_STAGES, sb = j & 1;
-                if (!mbar_wait(bar(B_K_FULL + slot), (j / K_STAGES) & 1)) return false;
-                if (!mbar_wait(bar(B_S_EMPTY + 2 * c + sb), ((j >> 1) & 1) ^ 1)) return false;
+            // S_c = Q_c K^T for chain c's step i, over whatever the chain's score columns hold
+            // (the product of its step before has read its P from there: the tensor cores
+            // run the instructions in the order they were issued)
+            auto issue_s = [&](int c, int i) -> bool {
+                const int t = key_tile(c, i), slot = t % K_STAGES;
+                if (!mbar_wait(bar(B_K_FULL + slot), (t / K_STAGES) & 1)) return false;
                 tc_fence_after();
                 const uint32_t k_src = k_smem + slot * K_STAGE;
+                const uint32_t q_src = q_smem + (P.two_tiles ? c * Q_BYTES : 0);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t q_off = c * Q_BYTES + (kk >> 2) * BLOCK + (kk & 3) * 32;
-                    const uint32_t k_off = (kk >> 2) * KBLOCK + (kk & 3) * 32;
-                    umma(tmem + COL_S + (2 * c + sb) * BN, umma_desc(q_smem + q_off),
-                         umma_desc(k_src + k_off), idesc_s, kk ? 1u : 0u);
+                    const uint32_t off = (kk >> 2) * BLOCK + (kk & 3) * 32;
+                    umma(tmem + COL_S + c * BN, umma_desc(q_src + off), umma_desc(k_src + off),
+                         idesc_s, kk ? 1u : 0u);
                 }
-                umma_commit(bar(B_S_FULL + 2 * c + sb));
-                if (c == CHAINS - 1) umma_commit(bar(B_K_EMPTY + slot));   // the keys are done with
+                umma_commit(bar(B_S_FULL + c));
+                // the keys are done with after the last chain that reads them
+                if (!P.two_tiles || c == chains - 1) umma_commit(bar(B_K_EMPTY + slot));
+                return true;
+            };
+            // O_c += P_c V for chain c's step i, P read from tensor memory
+            auto issue_pv = [&](int c, int i) -> bool {
+                const int t = key_tile(c, i), slot = t % V_STAGES;
+                if (!mbar_wait(bar(B_P_FULL + c), i & 1)) return false;
+                if (!mbar_wait(bar(B_V_FULL + slot), (t / V_STAGES) & 1)) return false;
+                tc_fence_after();
+                const uint32_t v_src = v_smem + slot * V_STAGE;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    umma_ts(tmem + COL_O + c * BN, tmem + COL_S + c * BN + kk * 8,
+                            umma_desc_mn(v_src + kk * 16 * 128, KBLOCK), idesc_o, (i | kk) ? 1u : 0u);
+                umma_commit(bar(B_O_REST + c));            // O_c holds step i
+                if (!P.two_tiles || c == chains - 1) umma_commit(bar(B_V_EMPTY + slot));
                 return true;
             };
             if (!mbar_wait(bar(B_Q_FULL), 0)) timed_out = true;
-            for (int c = 0; c < CHAINS && !timed_out && n_tiles > 0; ++c)
-                if (!issue_qk(c, 0)) timed_out = true;
-            for (int j = 0; j < n_tiles && !timed_out; ++j) {
-                for (int c = 0; c < CHAINS && !timed_out; ++c) {
-                    if (j + 1 < n_tiles && !issue_qk(c, j + 1)) {
+            for (int c = 0; c < chains && !timed_out; ++c)
+                if (n_steps[c] > 0 && !issue_s(c, 0)) timed_out = true;
+            const int most = max(n_steps[0], n_steps[1]);
+            for (int i = 0; i < most && !timed_out; ++i) {
+                for (int c = 0; c < chains; ++c) {
+                    if (i >= n_steps[c]) continue;
+                    if (!issue_pv(c, i) || (i + 1 < n_steps[c] && !issue_s(c, i + 1))) {
                         timed_out = true;
                         break;
                     }
-                    const int pb = j % P_BUFS;
-                    if (!mbar_wait(bar(B_P_FULL + P_BUFS * c + pb), (j / P_BUFS) & 1)) {
-                        timed_out = true;
-                        break;
-                    }
-                    if (c == 0 && !mbar_wait(bar(B_V_FULL + j % V_STAGES), (j / V_STAGES) & 1)) {
-                        timed_out = true;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t v_src = v_smem + (j % V_STAGES) * V_STAGE;
-#pragma unroll
-                    for (int kk = 0; kk < BN / 16; ++kk)
-                        umma(tmem + COL_O + c * HD,
-                             umma_desc(p_smem + (P_BUFS * c + pb) * P_BYTES + (kk >> 2) * BLOCK +
-                                       (kk & 3) * 32),
-                             umma_desc_mn(v_src + kk * 16 * 128, KBLOCK), idesc_o,
-                             (j | kk) ? 1u : 0u);
-                    umma_commit(bar(B_P_EMPTY + P_BUFS * c + pb));   // this P is free, O holds tile j
                 }
-                umma_commit(bar(B_V_EMPTY + (j % V_STAGES)));  // the values of tile j are done with
             }
         }
     } else {
         // ------------------------------------------------- softmax, correction, epilogue
-        // Warps w and w + 4 own the same 32 rows (TMEM lanes of quarter w % 4); the first
-        // takes keys 0..63 of a tile, the second keys 64..127, and of O and of Q each
-        // half of the columns.  A scheduler thus has two warps to issue from.  The pair
-        // meets once a tile (named barrier) to agree on the row maximum.
-        const int q = warp & 3;
-        const int half = (warp - 2) >> 2;                      // which half of the keys
-        const int row_in = q * 32 + lane;                      // row of the tile = TMEM lane
-        const int row = row0 + row_in;
-        constexpr int HB = BN / 2;                             // keys of a half
-        constexpr int HO = HD / 2;                             // columns of O of a half
-        const bool live = row < rows;
-        const int ti = live ? row / P.group : 0, g = live ? row - ti * P.group : 0;
+        // One thread a row: warps 2..5 are chain 0, warps 6..9 chain 1; a warp reaches the
+        // lanes of tensor memory of its quarter (warp index modulo four).
+        const int c = chain;
         const int pos = live ? pos0 + ti : -1;
         const int lo_row = P.window > 0 ? pos - P.window + 1 : 0;
-        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;\n" ::"r"(1 + q) : "memory"); };
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const uint32_t s_addr = tmem + lane_base + COL_S + c * BN;
+        const uint32_t o_addr = tmem + lane_base + COL_O + c * BN;
 
-        // this thread's half of its row of Q into shared memory, in the operand layout
+        // this thread's part of Q into shared memory, in the operand layout
         {
+            const uint32_t q_dst = q_smem + (P.two_tiles ? c * Q_BYTES : 0);
 #pragma unroll
-            for (int i = 0; i < HD / 16; ++i) {
-                const uint4 v = q_regs[i];
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
-                             ::"r"(swz(q_smem, row_in, half * (HD / 16) + i)),
-                               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            for (int i = 0; i < Q_CHUNKS; ++i) {
+                if (i < q_chunks) {
+                    const uint4 v = q_regs[i];
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
+                                 ::"r"(swz(q_dst, row_in, q_chunk0 + i)),
+                                   "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                }
             }
             fence_proxy_async();
             mbar_arrive(bar(B_Q_FULL));
         }
 
-        float m_used = -INFINITY, l = 0.f;                     // l: the sum over this half's keys
-        for (int j = 0; j < n_tiles && !timed_out; ++j) {
-            const int sb = j & 1;
-            const int kbase = kbase0 + j * BN + half * HB;     // first key of this half
-            if (!mbar_wait(bar(B_S_FULL + sb), (j >> 1) & 1)) {
+        float m_used = -INFINITY, l = 0.f;
+        const int steps = n_steps[c];
+        for (int i = 0; i < steps && !timed_out; ++i) {
+            const int kbase = kbase0 + key_tile(c, i) * BN;
+            if (!mbar_wait(bar(B_S_FULL + c), i & 1)) {
                 timed_out = true;
                 break;
             }
             tc_fence_after();
-            const uint32_t s_addr = tmem + lane_base + COL_S + sb * BN + half * HB;
-            // this half of the row of raw scores into registers (the scale to the log2
-            // domain is folded into the exponent's multiply-add); a key needs a mask only
-            // on the diagonal tiles and at a window's edge
-            float sc[HB];
+            // the row of raw scores into registers (the scale to the log2 domain is folded
+            // into the exponent's multiply-add); a key needs a mask only on the diagonal
+            // tiles and at a window's edge
+            float sc[BN];
 #pragma unroll
-            for (int c0 = 0; c0 < HB; c0 += 32) {
-                uint32_t a[16], b[16];
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t a[16];
                 tmem_ld16(s_addr + c0, a);
-                tmem_ld16(s_addr + c0 + 16, b);
-                tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    sc[c0 + e] = __uint_as_float(a[e]);
-                    sc[c0 + 16 + e] = __uint_as_float(b[e]);
-                }
+                for (int e = 0; e < 16; ++e) sc[c0 + e] = __uint_as_float(a[e]);
             }
-            // the scores are in registers: the tile after next may overwrite them
-            tc_fence_before();
-            mbar_arrive(bar(B_S_EMPTY + sb));
-            const bool masked = kbase + HB - 1 > pos || kbase < lo_row;
+            tmem_ld_wait();
+            const bool masked = kbase + BN - 1 > pos || kbase < lo_row;
             if (__any_sync(0xffffffffu, masked)) {
 #pragma unroll
-                for (int e = 0; e < HB; ++e) {
+                for (int e = 0; e < BN; ++e) {
                     const int jj = kbase + e;
                     if (jj > pos || jj < lo_row) sc[e] = -INFINITY;
                 }
@@ -378,29 +379,23 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
 #pragma unroll
             for (int e = 0; e < 8; ++e) mx[e] = sc[e];
 #pragma unroll
-            for (int e = 8; e < HB; ++e) mx[e & 7] = fmaxf(mx[e & 7], sc[e]);
-            const float m_half = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+            for (int e = 8; e < BN; ++e) mx[e & 7] = fmaxf(mx[e & 7], sc[e]);
+            const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
                                        fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))) *
                                  P.scale_log2;    // the scale is positive
-            // both halves' maxima: the row's maximum over the tile (slots alternate
-            // with the tile, so one meeting a tile is enough)
-            row_max[sb][half][row_in] = m_half;
-            pair_sync();
-            const float m_tile = fmaxf(row_max[sb][0][row_in], row_max[sb][1][row_in]);
             const bool grow = m_tile > m_used + RESCALE_STEP || (m_used == -INFINITY && m_tile > m_used);
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? m_tile : m_used;
                 const float cf = (grow && m_used != -INFINITY) ? fast_exp2(m_used - m_new) : 1.0f;
-                if (j > 0) {
-                    // O must be at rest: the product of the tile before has to be done
-                    if (!mbar_wait(bar(B_P_EMPTY + (j - 1) % P_BUFS), ((j - 1) / P_BUFS) & 1)) {
+                if (i > 0) {
+                    // O must be at rest: the product of the step before has to be done
+                    if (!mbar_wait(bar(B_O_REST + c), (i - 1) & 1)) {
                         timed_out = true;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t o_addr = tmem + lane_base + COL_O + half * HO;
 #pragma unroll
-                    for (int c0 = 0; c0 < HO; c0 += 32) {
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
                         uint32_t v[16], w[16];
                         tmem_ld16(o_addr + c0, v);
                         tmem_ld16(o_addr + c0 + 16, w);
@@ -413,72 +408,103 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                         tmem_st16(o_addr + c0, v);
                         tmem_st16(o_addr + c0 + 16, w);
                     }
-                    tmem_st_wait();
                 }
                 l *= cf;
                 m_used = m_new;
             }
-            // this tile's P buffer was last read by the product of the tile two before
-            const int pb = j % P_BUFS;
-            if (j >= P_BUFS && !mbar_wait(bar(B_P_EMPTY + pb), ((j / P_BUFS) & 1) ^ 1)) {
-                timed_out = true;
-                break;
-            }
-            // probabilities, their sum, and P as the next product's operand
+            // probabilities, their sum, and P over the scores as the next product's operand:
+            // keys 2j, 2j + 1 share column j
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
             float part[4] = {0.f, 0.f, 0.f, 0.f};             // four running sums
 #pragma unroll
-            for (int ch = 0; ch < HB / 8; ++ch) {
-                uint32_t pk[4];
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t pk[16];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float p0 = fast_exp2(fmaf(sc[ch * 8 + 2 * u], P.scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(sc[ch * 8 + 2 * u + 1], P.scale_log2, neg_m));
-                    part[u] += p0 + p1;
+                for (int u = 0; u < 16; ++u) {
+                    const float p0 = fast_exp2(fmaf(sc[c0 + 2 * u], P.scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(sc[c0 + 2 * u + 1], P.scale_log2, neg_m));
+                    part[u & 3] += p0 + p1;
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     pk[u] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n"
-                             ::"r"(swz(p_smem + pb * P_BYTES, row_in, half * (HB / 8) + ch)),
-                               "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+                tmem_st16(s_addr + c0 / 2, pk);
             }
             l += (part[0] + part[1]) + (part[2] + part[3]);
-            tc_fence_before();                 // a rescaled O is in place before the product adds to it
-            fence_proxy_async();
-            mbar_arrive(bar(B_P_FULL + pb));
+            tmem_st_wait();                    // P and a rescaled O are in place
+            tc_fence_before();
+            mbar_arrive(bar(B_P_FULL + c));
         }
-        // the row's sum is the two halves' sums (first half first); they meet in the
-        // slots the last tile did not use
-        float (*row_sum)[128] = row_max[n_tiles & 1];
-        row_sum[half][row_in] = l;
-        pair_sync();
-        const float l_row = row_sum[0][row_in] + row_sum[1][row_in];
-        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
-        // the last P V (the products end in the order they were issued), then the row's output
-        if (!timed_out && n_tiles > 0 &&
-            !mbar_wait(bar(B_P_EMPTY + (n_tiles - 1) % P_BUFS), ((n_tiles - 1) / P_BUFS) & 1))
+        // the chain's last product (the products end in the order they were issued)
+        if (!timed_out && steps > 0 && !mbar_wait(bar(B_O_REST + c), (steps - 1) & 1))
             timed_out = true;
         tc_fence_after();
-        __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
-                             (size_t)(kvh * P.group + g) * HD + half * HO;
-        uint32_t ov[HO / 16][16];                  // all loads under way, one wait
+        if (P.two_tiles) {
+            // the chain's rows are its own: O / l
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
+                                 (size_t)(kvh * P.group + g) * HD;
 #pragma unroll
-        for (int c0 = 0; c0 < HO; c0 += 16)
-            tmem_ld16(tmem + lane_base + COL_O + half * HO + c0, ov[c0 / 16]);
-        tmem_ld_wait();
-        if (live) {
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[16], w[16];
+                tmem_ld16(o_addr + c0, v);
+                tmem_ld16(o_addr + c0 + 16, w);
+                tmem_ld_wait();
+                if (live) {
+                    uint32_t o[16];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * e]) * inv,
+                                                                 __uint_as_float(v[2 * e + 1]) * inv);
+                        o[e] = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2bfloat162_rn(__uint_as_float(w[2 * e]) * inv,
+                                                  __uint_as_float(w[2 * e + 1]) * inv);
+                        o[8 + e] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+#pragma unroll
+                    for (int e = 0; e < 16; e += 4)
+                        *reinterpret_cast<uint4*>(dst + c0 + 2 * e) = make_uint4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+                }
+            }
+        } else {
+            // both chains hold the same rows over different keys: each thread merges its half
+            // of the columns from the two accumulators (chain 0's first)
+            chain_state[c][row_in] = make_float2(m_used, l);
+            tc_fence_before();
+            asm volatile("bar.sync 1, %0;\n" ::"n"(SOFTMAX_THREADS) : "memory");
+            tc_fence_after();
+            const float2 s0 = chain_state[0][row_in], s1 = chain_state[1][row_in];
+            const float m = fmaxf(s0.x, s1.x);
+            const float f0 = s0.x == -INFINITY ? 0.f : fast_exp2(s0.x - m);
+            const float f1 = s1.x == -INFINITY ? 0.f : fast_exp2(s1.x - m);
+            const float l_row = s0.y * f0 + s1.y * f1;
+            const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+            const float w0 = f0 * inv, w1 = f1 * inv;
+            const bool second = n_steps[1] > 0;            // else its accumulator was never written
+            constexpr int HO = HD / 2;
+            const uint32_t o0 = tmem + lane_base + COL_O + c * HO, o1 = o0 + BN;
+            __nv_bfloat16* dst = P.out + (size_t)(tok0 + ti) * P.n_heads * HD +
+                                 (size_t)(kvh * P.group + g) * HD + c * HO;
 #pragma unroll
             for (int c0 = 0; c0 < HO; c0 += 16) {
-                uint32_t w[8];
+                uint32_t v[16], w[16];
+                tmem_ld16(o0 + c0, v);
+                if (second) tmem_ld16(o1 + c0, w);
+                tmem_ld_wait();
+                if (live) {
+                    uint32_t o[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    __nv_bfloat162 h =
-                        __floats2bfloat162_rn(__uint_as_float(ov[c0 / 16][2 * e]) * inv,
-                                              __uint_as_float(ov[c0 / 16][2 * e + 1]) * inv);
-                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                    for (int e = 0; e < 8; ++e) {
+                        float a = __uint_as_float(v[2 * e]) * w0, b = __uint_as_float(v[2 * e + 1]) * w0;
+                        if (second) {
+                            a = fmaf(__uint_as_float(w[2 * e]), w1, a);
+                            b = fmaf(__uint_as_float(w[2 * e + 1]), w1, b);
+                        }
+                        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                        o[e] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
                 }
-                *reinterpret_cast<uint4*>(dst + c0) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
             }
         }
     }
@@ -512,26 +538,42 @@ bool pool_map(const void* pool, long long pool_rows, int block, CUtensorMap* out
     *out = it->second;
     return true;
 }
+
+// MLS_B200_ATTENTION_ROWS = 128 | 256 fixes the rows of a CTA (for measurements and tests);
+// mls_attention_tc_set_rows does the same at run time (0: choose by the step).
+int g_forced_rows = [] {
+    const char* v = getenv("MLS_B200_ATTENTION_ROWS");
+    return v ? atoi(v) : 0;
+}();
 }  // namespace
 #endif
+
+MLS_API void mls_attention_tc_set_rows(int rows) {
+#if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
+    g_forced_rows = rows;
+#endif
+}
 
 // Rows of one tile of mls_attention_tc (0: this head size has no such kernel).
 MLS_API int mls_attention_tc_rows() {
 #if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
-    return ROWS;
+    return CHAIN_ROWS;
 #else
     return 0;
 #endif
 }
 
-// Prompts and portions of a step: n_tiles = number of tiles of mls_attention_tc_rows() rows (requests that
-// the split kernel takes are left out when skip_small is set).  Returns
+// Prompts and portions of a step: n_tiles = number of tiles of mls_attention_tc_rows() rows
+// over the requests, n_tiles_wide = of twice as many rows (requests that the split kernel
+// takes are left out of both when skip_small is set).  A CTA takes a wide tile when those
+// give every SM one, else a tile whose keys it walks in two halves.  Returns
 // MLS_ERR_UNSUPPORTED (and launches nothing) for head or page sizes it does not take.
 MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, const void* v_pool,
                              const int* block_table, int max_blocks, const int* cu_q,
                              const int* ctx_len, int n_req, int n_heads, int n_kv, int block_size,
-                             float scale, int window, int n_tiles, int skip_small,
-                             long long pool_pages, int* status, cudaStream_t stream) {
+                             float scale, int window, int n_tiles, int n_tiles_wide,
+                             int skip_small, long long pool_pages, int* status,
+                             cudaStream_t stream) {
 #if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
     if (n_tiles <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv) return MLS_ERR_UNSUPPORTED;
@@ -563,11 +605,14 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     P.block_size = block_size;
     P.window = window;
     P.small_only = skip_small ? 1 : 0;
+    P.two_tiles = (n_tiles_wide > 0 && (long long)n_tiles_wide * n_kv >= sm_count()) ? 1 : 0;
+    if (g_forced_rows == CHAIN_ROWS) P.two_tiles = 0;
+    if (g_forced_rows == 2 * CHAIN_ROWS && n_tiles_wide > 0) P.two_tiles = 1;
     P.scale_log2 = scale * LOG2E;
     P.status = status;
     P.n_pages = pool_pages;
-    MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, n_tiles), dim3(THREADS), SMEM_BYTES, stream, P,
-               kmap, vmap, kmap_wide, vmap_wide);
+    MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),
+               dim3(THREADS), SMEM_BYTES, stream, P, kmap, vmap, kmap_wide, vmap_wide);
     return launch_status();
 #else
     return MLS_ERR_UNSUPPORTED;

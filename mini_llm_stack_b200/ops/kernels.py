@@ -130,6 +130,7 @@ class Ops:
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
+        self._attention_lib_handles: dict = {}
         self._attention_fused: dict = {}         # head size -> decode attention that also rotates
         self._tc_rows: dict = {}                 # head size -> rows of a tile of the tcgen05 kernel
         self._scratch: dict = {}
@@ -445,7 +446,7 @@ class Ops:
                        [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I,
                         _P, _P, _LL, _P, _I, _P])
             tc = _decl(lib, "mls_attention_tc",
-                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _LL, _P, _P])
+                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _LL, _P, _P])
             fused = _decl(lib, "mls_attention_decode_fused",
                           [_P, _I, _LL, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I,
                            _I, _I, _F, _I, _I, _P, _P, _LL, _P, _P])
@@ -454,6 +455,16 @@ class Ops:
             rows_fn.restype = ctypes.c_int
             self._tc_rows[hd] = int(rows_fn()) or 128
             self._attention_libs[hd] = (fn, tc)
+            self._attention_lib_handles[hd] = lib
+
+    def set_attention_rows(self, hd: int, rows: int) -> None:
+        """Fix the rows a CTA of the tcgen05 attention kernel owns: 256 (two row tiles),
+        128 (one, its keys in halves) or 0 (chosen by the step's size; the default)."""
+        _need(rows in (0, 128, 256), "set_attention_rows: 0, 128 or 256")
+        self.require_attention(hd)
+        lib = self._attention_lib_handles[hd]
+        fn = _decl(lib, "mls_attention_tc_set_rows", [_I], restype=None)
+        fn(rows)
 
     def attention_facts(self, hd: int) -> dict:
         """What a mixer needs to know of the attention kernels to plan a step's
@@ -475,8 +486,8 @@ class Ops:
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
                         scale: float, window: int, plan=None) -> None:
         """Attention of the step's tokens over the pages.  ``plan`` (the mixer's, from
-        ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` tiles of the requests that are
-        not small, ``any_small``, ``n_split`` context splits for the small ones."""
+        ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` / ``n_tiles_tc_wide`` tiles of the
+        requests that are not small, ``any_small``, ``n_split`` context splits for the small ones."""
         g = step.groups[cache.group]
         t = step.n_tokens
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
@@ -496,8 +507,8 @@ class Ops:
                 _check(tc(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
                           _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                           step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
-                          n_tiles_tc, n_small, cache.k_pool.shape[1], _ptr(self.status),
-                          self._stream()), "attention_tc")
+                          n_tiles_tc, plan.n_tiles_tc_wide, n_small, cache.k_pool.shape[1],
+                          _ptr(self.status), self._stream()), "attention_tc")
                 n_tiles = 0
                 if not n_small:
                     return

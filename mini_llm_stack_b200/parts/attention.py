@@ -25,6 +25,7 @@ class AttentionPlan:
     """How one step's attention is launched (for one shape of heads)."""
     n_tiles: int          # tiles of the mma.sync tile kernel over the requests that are not small
     n_tiles_tc: int       # tiles of the tcgen05 kernel over the same requests
+    n_tiles_tc_wide: int  # tiles of twice as many rows: the kernel takes these when they fill the SMs
     any_small: bool       # some request has so few rows that the context-split kernel takes it
     n_split: int          # parts the context of the small requests is cut into
 
@@ -122,6 +123,7 @@ class GroupedQueryAttention(Mixer):
             plan = AttentionPlan(
                 n_tiles=sum(-(-r // f["tile_rows"]) for r in big),
                 n_tiles_tc=sum(-(-r // f["tc_rows"]) for r in big),
+                n_tiles_tc_wide=sum(-(-r // (2 * f["tc_rows"])) for r in big),
                 any_small=n_small > 0, n_split=n_split)
             step.attn_tiles[key] = plan
         return plan

@@ -545,6 +545,28 @@ def test_attention_mixed_batch(rts, dtype, heads, kv, hd, block):
     assert (got - want).abs().max().item() <= attn_tol(dtype, 333) * want.abs().max().item()
 
 
+@pytest.mark.parametrize("rows", [128, 256])
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window", [None, 200])
+def test_prompt_attention_as_two_row_tiles_and_as_two_key_halves(rts, rows, hd, window):
+    """The tcgen05 prompt kernel's two ways to run two chains a CTA, each forced: 256 rows
+    whose two halves walk the key tiles together, or 128 rows whose keys are split in
+    halves.  Requests that end inside a row tile, inside a key tile, with one chain idle,
+    with chains of different length, and long enough for the rings of tiles to wrap."""
+    ops = rts[torch.bfloat16].ops
+    ctxs = [333, 45, 700, 64, 1300, 130]
+    q_lens = [70, 45, 300, 64, 515, 33]
+    case = AttnCase(rts[torch.bfloat16], 8, 2, hd, 16, ctxs, q_lens, window=window, seed=7 + hd)
+    ops.set_attention_rows(hd, rows)
+    try:
+        got = case.run()
+    finally:
+        ops.set_attention_rows(hd, 0)
+    ops.check_status()
+    want = case.want()
+    assert (got - want).abs().max().item() <= attn_tol(torch.bfloat16, 1300) * want.abs().max().item()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("ctx", [1, 15, 16, 17, 64, 65, 255, 256, 257, 1000, 3000])
 def test_attention_decode_at_page_and_tile_edges(rts, dtype, ctx):
