@@ -119,6 +119,27 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // head fit one 16-row tile.
 __device__ __forceinline__ bool is_small(int q_len, int group) { return q_len * group <= 16; }
 
+// Key tiles a context split holds: the tiles of the step's longest small request, shared out
+// over the splits.  Every request is cut at the same multiples, so a shorter one fills only
+// its first splits (the others find no tile and say so to the merge) and no CTA walks more
+// tiles than the longest request's.  All threads of the grid compute the same number from
+// the step's arrays.
+__device__ __forceinline__ int tiles_per_split(const int* cu_q, const int* ctx_len, int n_req,
+                                               int group, int window, int bn, int n_split) {
+    const int lane = threadIdx.x & 31;
+    int most = 1;
+    for (int r = lane; r < n_req; r += 32) {
+        const int q_len = cu_q[r + 1] - cu_q[r];
+        if (!is_small(q_len, group)) continue;
+        const int ctx = ctx_len[r], pos0 = ctx - q_len;
+        const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+        most = max(most, (ctx - 1 - (lo / bn) * bn) / bn + 1);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
+    return (most + n_split - 1) / n_split;
+}
+
 // Keys kbase .. kbase+63 of one kv head into shared memory; rows outside [lo, hi]
 // or on a released page are zero-filled, so nothing that is not a key of this
 // request can reach the products.
@@ -349,9 +370,11 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
     const int* table = P.block_table + (size_t)r * P.max_blocks;
     const int kbase0 = (lo / BN) * BN;
     const int tiles_all = (hi - kbase0) / BN + 1;
-    const int per = (tiles_all + P.n_split - 1) / P.n_split;
+    const int per = P.n_split == 1 ? tiles_all
+        : tiles_per_split(P.cu_q, P.ctx_len, P.n_req, P.group, P.window, BN, P.n_split);
     const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
     const int n_tiles = max(0, t_end - t_begin);
+    if (n_tiles == 0) return;                         // a stretch past the request's end: the merge knows
 
     const int rA = lane >> 2, rB = rA + 8;
     const int pA = rA < rows ? pos0 + rA / P.group : -1;
@@ -526,7 +549,19 @@ __global__ void attention_merge_kernel(const Params P) {
     // arrays were copied before its first kernel began)
     int r = 0;
     while (r + 1 < P.n_req && P.cu_q[r + 1] <= t) ++r;
-    const bool mine = is_small(P.cu_q[r + 1] - P.cu_q[r], P.group);
+    const int q_len = P.cu_q[r + 1] - P.cu_q[r];
+    const bool mine = is_small(q_len, P.group);
+    __shared__ int parts_here;
+    if (threadIdx.x < 32) {
+        // the stretches of this request that hold tiles: the others wrote nothing
+        const int per = tiles_per_split(P.cu_q, P.ctx_len, P.n_req, P.group, P.window, BN, P.n_split);
+        const int ctx = P.ctx_len[r];
+        const int lo = P.window > 0 ? max(0, ctx - q_len - P.window + 1) : 0;
+        const int tiles_all = (ctx - 1 - (lo / BN) * BN) / BN + 1;
+        if (threadIdx.x == 0) parts_here = min(P.n_split, (tiles_all + per - 1) / per);
+    }
+    __syncthreads();
+    const int n_parts = parts_here;
     chain_wait();
     if (!mine) return;
     const size_t units = (size_t)P.n_tokens * P.n_heads;
@@ -538,7 +573,7 @@ __global__ void attention_merge_kernel(const Params P) {
 #pragma unroll
         for (int i = 0; i < MAX_SPLITS / 32; ++i) {
             const int s = threadIdx.x + 32 * i;
-            lse[i] = s < P.n_split ? P.part_lse[s * units + unit] : -INFINITY;
+            lse[i] = s < n_parts ? P.part_lse[s * units + unit] : -INFINITY;
             m = fmaxf(m, lse[i]);
         }
         m = warp_max(m);
@@ -546,8 +581,8 @@ __global__ void attention_merge_kernel(const Params P) {
 #pragma unroll
         for (int i = 0; i < MAX_SPLITS / 32; ++i) {
             const int s = threadIdx.x + 32 * i;
-            const float w = (m == -INFINITY || s >= P.n_split) ? 0.f : fast_exp2(lse[i] - m);
-            if (s < P.n_split) weight[s] = w;
+            const float w = (m == -INFINITY || s >= n_parts) ? 0.f : fast_exp2(lse[i] - m);
+            if (s < n_parts) weight[s] = w;
             wsum += w;
         }
         wsum = warp_sum(wsum);
@@ -557,14 +592,14 @@ __global__ void attention_merge_kernel(const Params P) {
     const float wsum = total;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float acc = 0.f;
-        for (int s0 = 0; s0 < P.n_split; s0 += 8) {
+        for (int s0 = 0; s0 < n_parts; s0 += 8) {
             float o[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if (s0 + j < P.n_split) o[j] = P.part_o[((s0 + j) * units + unit) * HD + d];
+                if (s0 + j < n_parts) o[j] = P.part_o[((s0 + j) * units + unit) * HD + d];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if (s0 + j < P.n_split) acc += weight[s0 + j] * o[j];
+                if (s0 + j < n_parts) acc += weight[s0 + j] * o[j];
         }
         P.out[unit * HD + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
     }
@@ -699,9 +734,14 @@ attention_split_tma_kernel(const Params P, const Fused F,
     const int* table = P.block_table + (size_t)r * P.max_blocks;
     const int kbase0 = (lo / BN) * BN;
     const int tiles_all = (hi - kbase0) / BN + 1;
-    const int per = (tiles_all + P.n_split - 1) / P.n_split;
+    const int per = P.n_split == 1 ? tiles_all
+        : tiles_per_split(P.cu_q, P.ctx_len, P.n_req, P.group, P.window, BN, P.n_split);
     const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
     const int n_tiles = max(0, t_end - t_begin);
+    if (n_tiles == 0 && !P.cluster_merge) {           // a stretch past the request's end: the merge
+        chain_wait();                                 // kernel knows; inside a cluster it takes part
+        return;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TSTAGES; ++s) {

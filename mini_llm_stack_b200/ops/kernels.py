@@ -471,11 +471,13 @@ class Ops:
         launches: ``small_rows`` (requests whose (token, head) rows of one kv head are
         at most this many go to the context-split kernel), ``tile_rows`` and
         ``tc_rows`` (rows of a tile of the mma.sync and of the tcgen05 tile kernel),
-        ``split_slots`` (CTAs of the split kernel the GPU runs at a time: two an SM),
+        ``split_keys`` (keys of a tile of the split kernel), ``split_slots`` (CTAs of the
+        split kernel the GPU runs at a time: two an SM),
         ``cluster_splits`` (up to so many context splits are merged inside the kernel),
         ``tensor_cores`` (False: the one-warp-per-row kernel runs, which needs no plan)."""
         tma = self.attention_impl in ("auto", "mma") and hd % 64 == 0
         return {"small_rows": 16, "tile_rows": 64, "tc_rows": self._tc_rows.get(hd, 128),
+                "split_keys": 64,
                 "split_slots": 2 * self.sm_count,
                 # most context splits that merge inside the split kernel (a merge kernel
                 # takes over beyond that)

@@ -30,29 +30,34 @@ class AttentionPlan:
     n_split: int          # parts the context of the small requests is cut into
 
 
-def context_splits(n_small: int, longest: int, n_kv: int, slots: int = 296,
-                   cluster_splits: int = 0) -> int:
-    """Context splits for ``n_small`` decoding requests of up to ``longest`` keys.
+def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int = 0) -> int:
+    """Context splits for decoding requests of ``tiles[i]`` key tiles (64 keys) each.
 
-    ``slots`` CTAs of the split kernel run at a time (two an SM: 296 on a B200); the cost
-    of a choice is its number of such waves times the 64-key tiles a CTA walks (plus six
-    tiles' worth of start-up), plus the merge kernel's time, which grows with the number
-    of parts (measured at batch 1: 16 parts beat 32).  Up to ``cluster_splits`` parts are
-    merged inside the split kernel while one round of CTAs holds them all; beyond that a
-    merge kernel follows, which costs about what two tiles take.  The cheapest choice
-    wins; a split is never shorter than 256 keys.
+    The kernel cuts every request at the same multiples of tiles, the longest request's
+    tiles shared out over the splits: a shorter request fills only its first splits, and
+    the CTAs of the others leave at once.  ``slots`` CTAs of the split kernel run at a
+    time (two an SM: 296 on a B200); the cost of a choice is its number of such waves of
+    CTAs that have tiles times the tiles a CTA walks (plus six tiles' worth of start-up),
+    plus what placing the empty CTAs costs, plus the merge's time, which grows with the
+    number of parts (measured at batch 1: 16 parts beat 32).  Up to ``cluster_splits``
+    parts are merged inside the split kernel while one round of CTAs holds them all;
+    beyond that a merge kernel follows, which costs about what two tiles take.  The
+    cheapest choice wins; a split is never shorter than 256 keys.
     """
+    longest = max(tiles)
     forced = os.environ.get("MLS_B200_SPLITS")
     if forced:
-        return max(1, min(int(forced), max(1, longest // 64)))
-    pairs = max(1, n_small * n_kv)
-    tiles = -(-longest // 64)
+        return max(1, min(int(forced), longest))
     best, best_cost = 1, None
-    for s in range(1, max(1, min(64, longest // 256)) + 1):
-        waves = -(-pairs * s // slots)
-        cost = waves * (-(-tiles // s) + 6) + (0.3 * s if s > 1 else 0.0)
-        if s > 1 and cluster_splits and not (s <= cluster_splits and pairs * s <= slots):
-            cost += 2.0
+    for s in range(1, max(1, min(64, longest // 4)) + 1):
+        per = -(-longest // s)
+        busy = sum(-(-t // per) for t in tiles) * n_kv
+        grid = len(tiles) * n_kv * s
+        cost = -(-busy // slots) * (per + 6) + 2.0 * (grid - busy) / slots
+        if s > 1:
+            cost += 0.3 * s
+            if not (cluster_splits and s <= cluster_splits and grid <= slots):
+                cost += 2.0
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
@@ -117,8 +122,9 @@ class GroupedQueryAttention(Mixer):
             n_small = sum(small)
             n_split = 1
             if n_small:
-                longest = max(c for c, s in zip(step.ctx_lens, small) if s)
-                n_split = context_splits(n_small, longest, self.n_kv_heads, f["split_slots"],
+                keys = f.get("split_keys", 64)
+                tiles = [-(-c // keys) for c, s in zip(step.ctx_lens, small) if s]
+                n_split = context_splits(tiles, self.n_kv_heads, f["split_slots"],
                                          f.get("cluster_splits", 0))
             plan = AttentionPlan(
                 n_tiles=sum(-(-r // f["tile_rows"]) for r in big),

@@ -686,14 +686,19 @@ def test_window_edge_with_heads_of_64_and_128(rts, heads, kv, hd, window, ctx, q
 
 @pytest.mark.parametrize("hd, heads, kv", [(64, 8, 2), (128, 32, 8)])
 @pytest.mark.parametrize("splits", [1, 2, 3, 5, 8, 12])
-def test_context_splits_merge_in_clusters_and_by_kernel(rts, monkeypatch, hd, heads, kv, splits):
+@pytest.mark.parametrize("window", [None, 700])
+def test_context_splits_merge_in_clusters_and_by_kernel(rts, monkeypatch, hd, heads, kv, splits,
+                                                        window):
     """Decoded tokens over contexts cut into a forced number of stretches: two to eight
     stretches are merged inside clusters of the split kernel (through the CTAs' shared
-    memory), more by the merge kernel; requests of very different lengths, so that some
-    stretches are empty."""
+    memory), more by the merge kernel.  Every request is cut at the same multiples of
+    tiles (the longest request's, shared out over the stretches): the requests are of very
+    different lengths, so the shorter ones fill only their first stretches, with and
+    without a window that moves each request's first tile."""
     monkeypatch.setenv("MLS_B200_SPLITS", str(splits))
     rt = rts[torch.bfloat16]
-    case = AttnCase(rt, heads, kv, hd, 16, [3000, 70, 1025, 1, 640], [1, 1, 1, 1, 2], seed=31)
+    case = AttnCase(rt, heads, kv, hd, 16, [3000, 70, 1025, 1, 640], [1, 1, 1, 1, 2], window=window,
+                    seed=31)
     got, want = case.run(), case.want()
     rt.ops.check_status()
     assert bool(torch.isfinite(got).all())
