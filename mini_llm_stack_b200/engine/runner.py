@@ -139,43 +139,59 @@ class ModelRunner:
         self.steps += 1
         return logits
 
+    GRAPHS_KEPT = 48             # captured steps kept; the oldest goes first
+    PROMPT_SHAPE_SEEN = 3        # a step with portions is captured when its shape comes this often
+
     def _may_replay(self, ctx) -> bool:
-        """A step of single decoded tokens, all wanted, of a model whose parts all
-        agree to be captured."""
-        return (self.cuda_graphs and ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens
-                and self.model.decode_capturable)
+        """A step of single decoded tokens, all wanted, of a model whose parts all agree
+        to be captured; or any other step, if they all agree to that too."""
+        if not self.cuda_graphs:
+            return False
+        if ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens:
+            return self.model.decode_capturable
+        return self.model.prompt_capturable
 
     def _decode_from_graph(self, ctx):
-        """A step of single decoded tokens, replayed from a CUDA graph.
+        """A step replayed from a CUDA graph.
 
-        Such a step launches the same kernels with the same arguments whenever
-        the number of requests and what the parts add to the key (the attention's
-        cut of the context) are the same; only
-        the arrays the batch builder has just copied to the device differ, and
-        they lie at the same addresses.  The first step of a kind runs eagerly
-        (which sizes every buffer), the second is captured, later ones replay.
+        A step launches the same kernels with the same arguments whenever the requests'
+        token counts, the number of wanted rows and what the parts add to the key (the
+        attention's cut of the context) are the same; only the arrays the batch builder
+        has just copied to the device differ, and they lie at the same addresses.  The
+        first step of a kind runs eagerly (which sizes every buffer), the second is
+        captured, later ones replay; a step with portions of prompts, whose shape may
+        never come again, is captured when it has come ``PROMPT_SHAPE_SEEN`` times.
         """
         ops = self.runtime.ops
         moved = (ops.generation, self.builder.generation)
         if moved != self._graphs.get("moved"):
             self._graphs = {"moved": moved}      # a buffer moved: the old graphs are stale
-        key = (ctx.n_requests, self.model.decode_graph_key(ctx))
-        entry = self._graphs.get(key)
-        if entry is None:
-            self._graphs[key] = "warm"
-            return self.model.forward(ctx, self.handles)
-        if entry == "warm":
+        decoding = ctx.max_q_len == 1
+        shape = ctx.n_requests if decoding else tuple(ctx.q_lens)
+        key = (shape, ctx.n_out, self.model.decode_graph_key(ctx))
+        entry = self._graphs.pop(key, None)      # taken out and put back: the dict's order is by use
+        if entry is None or isinstance(entry, int):
+            seen = (entry or 0) + 1
+            if seen < (2 if decoding else self.PROMPT_SHAPE_SEEN):
+                self._keep(key, seen)
+                return self.model.forward(ctx, self.handles)
             before = (ops.launches, ops.library_launches)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx, self.handles)
             entry = (graph, logits, ops.launches - before[0], ops.library_launches - before[1])
-            self._graphs[key] = entry
+        self._keep(key, entry)
         graph, logits, own, lib = entry
         graph.replay()
         ops.launches += own
         ops.library_launches += lib
         return logits
+
+    def _keep(self, key, entry) -> None:
+        self._graphs[key] = entry
+        while len(self._graphs) > self.GRAPHS_KEPT + 1:          # + 1: the "moved" word
+            oldest = next(k for k in self._graphs if k != "moved")
+            del self._graphs[oldest]
 
     def release(self, owner) -> None:
         if self.cache.has(owner):

@@ -26,6 +26,11 @@ _ERRORS = {100001: "a size this kernel does not support",
            100002: "the driver refused to encode a tensor map"}
 
 
+# torch's own fast path to the current stream's handle (a C call without the argument
+# handling of torch.cuda.current_stream, which costs several microseconds a launch)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -112,6 +117,8 @@ class Ops:
                 "this engine runs on a CUDA device only (sm_100a kernels); "
                 f"device {device!r} is not one and there is no CPU path")
         self.act_dtype = act_dtype
+        self._device_index = (self.device.index if self.device.index is not None
+                              else torch.cuda.current_device())
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._libs: list = []                    # every kernel library in use
         self._chained = True                     # what the libraries were last told
@@ -134,6 +141,7 @@ class Ops:
         self._attention_fused: dict = {}         # head size -> decode attention that also rotates
         self._tc_rows: dict = {}                 # head size -> rows of a tile of the tcgen05 kernel
         self._scratch: dict = {}
+        self._transposed: dict = {}              # id(weight) -> (weight, its transposed view)
         self._gemm = None
         self._tiles_set = False
         self._parts_busy = False
@@ -174,6 +182,10 @@ class Ops:
         return buf
 
     def _stream(self):
+        """The raw handle of torch's current stream on this device (asked for at every
+        launch: a captured step runs on the capture's stream)."""
+        if _raw_stream is not None:
+            return _raw_stream(self._device_index)
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def check_status(self) -> None:
@@ -275,10 +287,13 @@ class Ops:
             self._gemm_bf16(a16, w, out, m, n, k)
             return
         self.library_launches += 1
+        held = self._transposed.get(id(w))           # the view costs a microsecond a call
+        if held is None or held[0] is not w:
+            held = self._transposed[id(w)] = (w, w.t())
         if out.dtype == torch.float32:
-            torch.mm(a16, w.t(), out_dtype=torch.float32, out=out)
+            torch.mm(a16, held[1], out_dtype=torch.float32, out=out)
         else:
-            torch.mm(a16, w.t(), out=out)
+            torch.mm(a16, held[1], out=out)
 
     def _use_own_gemm(self, m: int, n: int, k: int) -> bool:
         """The tcgen05 kernel takes rows that are whole 16-byte chunks; the choice
@@ -628,9 +643,14 @@ class Runtime:
         self.act_dtype = dtype
         self.ops = Ops(self.device, dtype)
         self._buffers: dict = {}
+        self._views: dict = {}               # (tag, dtype, shape) -> the view handed out last time
 
     def buffer(self, tag: str, shape: tuple, dtype: torch.dtype):
         """A step buffer: the same memory for the same tag, grown when needed."""
+        shape = tuple(shape)
+        view = self._views.get((tag, dtype, shape))
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -640,4 +660,10 @@ class Runtime:
             flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._buffers[key] = flat
             self.ops.generation += 1       # captured graphs point at the old memory
-        return flat[:n].view(shape)
+            for old in [k for k in self._views if k[0] == tag and k[1] == dtype]:
+                del self._views[old]
+        view = flat[:n].view(shape)
+        if len(self._views) > 4096:          # many shapes have come and gone
+            self._views.clear()
+        self._views[(tag, dtype, shape)] = view
+        return view

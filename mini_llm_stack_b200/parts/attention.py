@@ -103,6 +103,10 @@ class GroupedQueryAttention(Mixer):
         """Forward only launches kernels; the position part has to agree."""
         return bool(getattr(self.position, "decode_capturable", False))
 
+    @property
+    def prompt_capturable(self) -> bool:
+        return bool(getattr(self.position, "prompt_capturable", False))
+
     def plan(self, step: StepContext):
         """This step's ``AttentionPlan`` (None where the kernel in use needs none).
 

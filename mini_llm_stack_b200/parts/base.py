@@ -165,12 +165,15 @@ class Part:
     step of single decoded tokens from a graph only if every part of the model says
     ``decode_capturable`` (its ``forward`` then only launches work on the current
     stream: no wait for the device, no read of device memory by the host, no launch
-    that depends on values computed on the device) and keys the graph by the number of
-    requests plus what each part's ``decode_graph_key(step)`` adds (whatever else, known
-    on the host, changes its launches).  A part that says nothing is never captured.
+    that depends on values computed on the device) and keys the graph by the requests'
+    token counts plus what each part's ``decode_graph_key(step)`` adds (whatever else,
+    known on the host, changes its launches).  A step with portions of prompts is replayed
+    (once its shape has come three times) only if every part says ``prompt_capturable``:
+    the same promise for any step.  A part that says nothing is never captured.
     """
 
     decode_capturable = False
+    prompt_capturable = False
 
     def tensor_specs(self) -> dict:
         return {}

@@ -42,6 +42,10 @@ class PreNormBlock(Part):
     def decode_capturable(self) -> bool:
         return all(getattr(p, "decode_capturable", False) for _, p in self._named_parts())
 
+    @property
+    def prompt_capturable(self) -> bool:
+        return all(getattr(p, "prompt_capturable", False) for _, p in self._named_parts())
+
     def decode_graph_key(self, step: StepContext) -> tuple:
         return tuple(k for _, p in self._named_parts() if (k := p.decode_graph_key(step)))
 

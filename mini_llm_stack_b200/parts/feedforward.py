@@ -14,7 +14,7 @@ from .base import FeedForward, StepContext, TensorSpec
 
 
 class SwiGLUFeedForward(FeedForward):
-    decode_capturable = True      # forward only launches kernels on the current stream
+    decode_capturable = prompt_capturable = True   # forward only launches kernels on the current stream
 
     def __init__(self, d_model: int, intermediate_size: int):
         self.d_model, self.intermediate_size = int(d_model), int(intermediate_size)

@@ -25,7 +25,7 @@ class LayerCall:
 class TokenEmbedding(Part):
     """``x[t] = E[token[t]]``; no scaling, no position term (train/model.py:239)."""
 
-    decode_capturable = True
+    decode_capturable = prompt_capturable = True
 
     def __init__(self, vocab_size: int, d_model: int):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
@@ -48,7 +48,7 @@ class TokenEmbedding(Part):
 class OutputHead(Part):
     """``logits = h @ W^T`` in float32; W is the embedding table when tied."""
 
-    decode_capturable = True
+    decode_capturable = prompt_capturable = True
 
     def __init__(self, vocab_size: int, d_model: int, tied_to: Optional[TokenEmbedding]):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
@@ -149,6 +149,11 @@ class ComposedModel:
         """Whether a step of single decoded tokens may be replayed from a CUDA graph:
         only if every part says so (``Part.decode_capturable``)."""
         return all(getattr(p, "decode_capturable", False) for p in self._all_parts())
+
+    @property
+    def prompt_capturable(self) -> bool:
+        """The same for a step of any shape (``Part.prompt_capturable``)."""
+        return all(getattr(p, "prompt_capturable", False) for p in self._all_parts())
 
     def decode_graph_key(self, step: StepContext) -> tuple:
         """What the parts add to the key of a decode step's graph, without repeats."""

@@ -13,7 +13,7 @@ from .base import Norm, ResidualStream, TensorSpec
 
 
 class RMSNorm(Norm):
-    decode_capturable = True      # forward only launches kernels on the current stream
+    decode_capturable = prompt_capturable = True   # forward only launches kernels on the current stream
 
     def __init__(self, dim: int, eps: float):
         self.dim = int(dim)

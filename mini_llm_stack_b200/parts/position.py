@@ -26,7 +26,7 @@ def rotary_tables(head_dim: int, max_positions: int, theta: float):
 
 
 class RotaryPosition(PositionEncoding):
-    decode_capturable = True      # forward only launches kernels on the current stream
+    decode_capturable = prompt_capturable = True   # forward only launches kernels on the current stream
     applies_to = "qk"
 
     def __init__(self, head_dim: int, theta: float, max_positions: int):

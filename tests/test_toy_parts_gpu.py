@@ -220,7 +220,7 @@ def test_toy_mixer_through_the_scheduler_with_graphs_and_preemption(tmp_path, ca
         captured = [k for k, v in eng.runner._graphs.items()
                     if k != "moved" and isinstance(v, tuple)]
         if capturable:
-            assert captured and all(repr(("decay", cfg.d_model)) in repr(k[1]) for k in captured)
+            assert captured and all(repr(("decay", cfg.d_model)) in repr(k) for k in captured)
         else:
             assert not captured
         for p, g in zip(prompts, got):
