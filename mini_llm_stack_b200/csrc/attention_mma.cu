@@ -119,25 +119,19 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // head fit one 16-row tile.
 __device__ __forceinline__ bool is_small(int q_len, int group) { return q_len * group <= 16; }
 
-// Key tiles a context split holds: the tiles of the step's longest small request, shared out
-// over the splits.  Every request is cut at the same multiples, so a shorter one fills only
-// its first splits (the others find no tile and say so to the merge) and no CTA walks more
-// tiles than the longest request's.  All threads of the grid compute the same number from
-// the step's arrays.
-__device__ __forceinline__ int tiles_per_split(const int* cu_q, const int* ctx_len, int n_req,
-                                               int group, int window, int bn, int n_split) {
-    const int lane = threadIdx.x & 31;
-    int most = 1;
-    for (int r = lane; r < n_req; r += 32) {
-        const int q_len = cu_q[r + 1] - cu_q[r];
-        if (!is_small(q_len, group)) continue;
-        const int ctx = ctx_len[r], pos0 = ctx - q_len;
-        const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
-        most = max(most, (ctx - 1 - (lo / bn) * bn) / bn + 1);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
-    return (most + n_split - 1) / n_split;
+// Key tiles a context split holds: the most tiles a small request of this step can have,
+// shared out over the splits.  Every request is cut at the same multiples, so a shorter one
+// fills only its first splits (the others find no tile; the merge knows) and no CTA walks more
+// tiles than the longest request's.  The step's longest context lies one past the requests'
+// in ctx_len (the batch builder puts it there): all threads of the grid, and the merge
+// kernel, work the same number out from it, also when a captured step is replayed with
+// longer contexts.  With a window a small request (at most 16 new tokens) sees at most
+// window + 15 keys, which begin anywhere in a tile.
+__device__ __forceinline__ int tiles_per_split(const int* ctx_len, int n_req, int window, int bn,
+                                               int n_split) {
+    int most = (ctx_len[n_req] + bn - 1) / bn;
+    if (window > 0) most = min(most, (window + 15 + bn - 2) / bn + 1);
+    return (max(most, 1) + n_split - 1) / n_split;
 }
 
 // Keys kbase .. kbase+63 of one kv head into shared memory; rows outside [lo, hi]
@@ -371,7 +365,7 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
     const int kbase0 = (lo / BN) * BN;
     const int tiles_all = (hi - kbase0) / BN + 1;
     const int per = P.n_split == 1 ? tiles_all
-        : tiles_per_split(P.cu_q, P.ctx_len, P.n_req, P.group, P.window, BN, P.n_split);
+        : tiles_per_split(P.ctx_len, P.n_req, P.window, BN, P.n_split);
     const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
     const int n_tiles = max(0, t_end - t_begin);
     if (n_tiles == 0) return;                         // a stretch past the request's end: the merge knows
@@ -554,7 +548,7 @@ __global__ void attention_merge_kernel(const Params P) {
     __shared__ int parts_here;
     if (threadIdx.x < 32) {
         // the stretches of this request that hold tiles: the others wrote nothing
-        const int per = tiles_per_split(P.cu_q, P.ctx_len, P.n_req, P.group, P.window, BN, P.n_split);
+        const int per = tiles_per_split(P.ctx_len, P.n_req, P.window, BN, P.n_split);
         const int ctx = P.ctx_len[r];
         const int lo = P.window > 0 ? max(0, ctx - q_len - P.window + 1) : 0;
         const int tiles_all = (ctx - 1 - (lo / BN) * BN) / BN + 1;
@@ -735,7 +729,7 @@ attention_split_tma_kernel(const Params P, const Fused F,
     const int kbase0 = (lo / BN) * BN;
     const int tiles_all = (hi - kbase0) / BN + 1;
     const int per = P.n_split == 1 ? tiles_all
-        : tiles_per_split(P.cu_q, P.ctx_len, P.n_req, P.group, P.window, BN, P.n_split);
+        : tiles_per_split(P.ctx_len, P.n_req, P.window, BN, P.n_split);
     const int t_begin = split * per, t_end = min(tiles_all, t_begin + per);
     const int n_tiles = max(0, t_end - t_begin);
     if (n_tiles == 0 && !P.cluster_merge) {           // a stretch past the request's end: the merge

@@ -123,7 +123,7 @@ class BatchBuilder:
         cur = 0
         for name, n in (("token_ids", t_total), ("positions", t_total),
                         ("req_of_token", t_total), ("cu_q", r_total + 1),
-                        ("ctx_len", r_total), ("state_slot", r_total),
+                        ("ctx_len", r_total + 1), ("state_slot", r_total),
                         ("out_rows", max(n_out, 1))):
             off[name] = (cur, n)
             cur += _align(n)
@@ -151,7 +151,8 @@ class BatchBuilder:
         cu = np.zeros(r_total + 1, np.int64)
         np.cumsum(q_lens, out=cu[1:])
         view("cu_q")[:] = cu
-        view("ctx_len")[:] = ctx_lens
+        view("ctx_len")[:r_total] = ctx_lens
+        view("ctx_len")[r_total] = max(ctx_lens)     # one past the requests: the longest context
         view("state_slot")[:] = rows
         pos = view("positions")
         rot = view("req_of_token")

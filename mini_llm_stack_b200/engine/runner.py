@@ -13,6 +13,9 @@ as one batch and returns float32 logits at the wanted places only.
 
 from __future__ import annotations
 
+import os
+import time
+
 import torch
 
 from ..cache.manager import CacheError, CacheManager
@@ -72,6 +75,32 @@ def random_model(config, seed: int, norm_std: float = 0.0, dtype: str | None = N
     return model
 
 
+class _Seen:
+    """A step shape that has not been captured: how often it came, and how long the host
+    took to issue it against how long the GPU took to run it."""
+
+    __slots__ = ("count", "host_ms", "events")
+
+    def __init__(self):
+        self.count, self.host_ms, self.events = 0, 0.0, None
+
+    def timed(self, forward):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        t0 = time.perf_counter()
+        out = forward()
+        self.host_ms = (time.perf_counter() - t0) * 1e3
+        end.record()
+        self.events = (start, end)
+        return out
+
+    def host_bound(self, share: float) -> bool:
+        """Whether the last timed run was bound by the host (False while it still runs)."""
+        if self.events is None or not self.events[1].query():
+            return False
+        return self.host_ms >= share * self.events[0].elapsed_time(self.events[1])
+
+
 class ModelRunner:
     """A bound model, its cache and the step function over both."""
 
@@ -79,6 +108,8 @@ class ModelRunner:
                  cuda_graphs: bool = True):
         self.model = model
         self.cuda_graphs = cuda_graphs
+        # MLS_B200_PROMPT_GRAPHS=0: only steps of single decoded tokens replay from graphs
+        self.prompt_graphs = os.environ.get("MLS_B200_PROMPT_GRAPHS", "1") != "0"
         self._graphs: dict = {}
         self.runtime = model.runtime
         cfg = model.config
@@ -141,6 +172,7 @@ class ModelRunner:
 
     GRAPHS_KEPT = 48             # captured steps kept; the oldest goes first
     PROMPT_SHAPE_SEEN = 3        # a step with portions is captured when its shape comes this often
+    HOST_BOUND = 0.5             # ... and issuing it took the host this share of its time on the GPU
 
     def _may_replay(self, ctx) -> bool:
         """A step of single decoded tokens, all wanted, of a model whose parts all agree
@@ -149,7 +181,7 @@ class ModelRunner:
             return False
         if ctx.max_q_len == 1 and ctx.n_out == ctx.n_tokens:
             return self.model.decode_capturable
-        return self.model.prompt_capturable
+        return self.prompt_graphs and self.model.prompt_capturable
 
     def _decode_from_graph(self, ctx):
         """A step replayed from a CUDA graph.
@@ -159,8 +191,11 @@ class ModelRunner:
         attention's cut of the context) are the same; only the arrays the batch builder
         has just copied to the device differ, and they lie at the same addresses.  The
         first step of a kind runs eagerly (which sizes every buffer), the second is
-        captured, later ones replay; a step with portions of prompts, whose shape may
-        never come again, is captured when it has come ``PROMPT_SHAPE_SEEN`` times.
+        captured, later ones replay.  A step with portions of prompts, whose shape may
+        never come again, is captured when it has come ``PROMPT_SHAPE_SEEN`` times and
+        the host was what it waited for: issuing its kernels one by one took at least
+        ``HOST_BOUND`` of the time the GPU spent on them (small models, short portions).
+        A large step gains nothing from a graph.
         """
         ops = self.runtime.ops
         moved = (ops.generation, self.builder.generation)
@@ -170,11 +205,18 @@ class ModelRunner:
         shape = ctx.n_requests if decoding else tuple(ctx.q_lens)
         key = (shape, ctx.n_out, self.model.decode_graph_key(ctx))
         entry = self._graphs.pop(key, None)      # taken out and put back: the dict's order is by use
-        if entry is None or isinstance(entry, int):
-            seen = (entry or 0) + 1
-            if seen < (2 if decoding else self.PROMPT_SHAPE_SEEN):
+        if not isinstance(entry, tuple):
+            seen = entry or _Seen()
+            seen.count += 1
+            if decoding:
+                capture = seen.count >= 2
+            else:
+                capture = seen.count >= self.PROMPT_SHAPE_SEEN and seen.host_bound(self.HOST_BOUND)
+            if not capture:
                 self._keep(key, seen)
-                return self.model.forward(ctx, self.handles)
+                if decoding:
+                    return self.model.forward(ctx, self.handles)
+                return seen.timed(lambda: self.model.forward(ctx, self.handles))
             before = (ops.launches, ops.library_launches)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):

@@ -30,12 +30,14 @@ class AttentionPlan:
     n_split: int          # parts the context of the small requests is cut into
 
 
-def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int = 0) -> int:
+def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int = 0,
+                   longest: int = 0) -> int:
     """Context splits for decoding requests of ``tiles[i]`` key tiles (64 keys) each.
 
-    The kernel cuts every request at the same multiples of tiles, the longest request's
-    tiles shared out over the splits: a shorter request fills only its first splits, and
-    the CTAs of the others leave at once.  ``slots`` CTAs of the split kernel run at a
+    The kernel cuts every request at the same multiples of tiles, the tiles of the step's
+    longest context (``longest``, if a request that is not among these has more) shared
+    out over the splits: a shorter request fills only its first splits, and the CTAs of
+    the others leave at once.  ``slots`` CTAs of the split kernel run at a
     time (two an SM: 296 on a B200); the cost of a choice is its number of such waves of
     CTAs that have tiles times the tiles a CTA walks (plus six tiles' worth of start-up),
     plus what placing the empty CTAs costs, plus the merge's time, which grows with the
@@ -44,7 +46,7 @@ def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int
     beyond that a merge kernel follows, which costs about what two tiles take.  The
     cheapest choice wins; a split is never shorter than 256 keys.
     """
-    longest = max(tiles)
+    longest = max(longest, max(tiles))
     forced = os.environ.get("MLS_B200_SPLITS")
     if forced:
         return max(1, min(int(forced), longest))
@@ -129,7 +131,8 @@ class GroupedQueryAttention(Mixer):
                 keys = f.get("split_keys", 64)
                 tiles = [-(-c // keys) for c, s in zip(step.ctx_lens, small) if s]
                 n_split = context_splits(tiles, self.n_kv_heads, f["split_slots"],
-                                         f.get("cluster_splits", 0))
+                                         f.get("cluster_splits", 0),
+                                         longest=-(-step.max_ctx_len // keys))
             plan = AttentionPlan(
                 n_tiles=sum(-(-r // f["tile_rows"]) for r in big),
                 n_tiles_tc=sum(-(-r // f["tc_rows"]) for r in big),

@@ -94,7 +94,7 @@ class StepContext:
     positions: torch.Tensor          # [T] int32
     req_of_token: torch.Tensor       # [T] int32
     cu_q: torch.Tensor               # [R+1] int32
-    ctx_len: torch.Tensor            # [R] int32
+    ctx_len: torch.Tensor            # [R+1] int32: the requests', then the longest of them
     state_slot: torch.Tensor         # [R] int32
     out_rows: torch.Tensor           # [n_out] int32
     n_out: int
