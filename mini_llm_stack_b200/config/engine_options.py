@@ -28,7 +28,7 @@ class EngineOptions:
     device: str = "cuda:0"
     kv_dtype: str | None = None       # type of the cached keys and values; None: the run's dtype
     seed: int = 0                     # sampling seed of requests that bring none
-    cuda_graphs: bool = True          # replay pure-decode steps from a graph
+    cuda_graphs: bool = True          # replay decode steps (and repeated, host-bound prompt steps) from graphs
     launch_ahead: bool = True         # start the next decode step before the host has this one's tokens
 
     def __post_init__(self):
