@@ -1562,3 +1562,26 @@ MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long lon
 }
 
 MLS_API int mls_attention_head_dim() { return HD; }
+
+// CTAs of the context-split kernel that one SM holds at a time (registers and shared memory
+// decide: two at head size 128, more at smaller heads); use_tma as in mls_attention_mma.
+// 0 if the driver cannot say.
+MLS_API int mls_attention_split_ctas_per_sm(int use_tma) {
+    int n = 0;
+#if MLS_HEAD_DIM % 64 == 0
+    if (use_tma) {
+        if (cudaFuncSetAttribute(attention_split_tma_kernel,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, TMA_SMEM) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_split_tma_kernel, TMA_THREADS,
+                                                          TMA_SMEM) != cudaSuccess)
+            return 0;
+        return n;
+    }
+#endif
+    if (cudaFuncSetAttribute(attention_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SPLIT_SMEM) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_split_kernel, NT, SPLIT_SMEM) !=
+            cudaSuccess)
+        return 0;
+    return n;
+}

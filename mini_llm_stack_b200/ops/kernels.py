@@ -138,6 +138,7 @@ class Ops:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
         self._attention_lib_handles: dict = {}
+        self._split_ctas_per_sm: dict = {}       # head size -> CTAs of the split kernel an SM holds
         self._attention_fused: dict = {}         # head size -> decode attention that also rotates
         self._tc_rows: dict = {}                 # head size -> rows of a tile of the tcgen05 kernel
         self._scratch: dict = {}
@@ -471,6 +472,9 @@ class Ops:
             self._tc_rows[hd] = int(rows_fn()) or 128
             self._attention_libs[hd] = (fn, tc)
             self._attention_lib_handles[hd] = lib
+            per_sm = _decl(lib, "mls_attention_split_ctas_per_sm", [_I])
+            tma = self.attention_impl in ("auto", "mma") and hd % 64 == 0
+            self._split_ctas_per_sm[hd] = int(per_sm(1 if tma else 0)) or 2
 
     def set_attention_rows(self, hd: int, rows: int) -> None:
         """Fix the rows a CTA of the tcgen05 attention kernel owns: 256 (two row tiles),
@@ -487,13 +491,15 @@ class Ops:
         at most this many go to the context-split kernel), ``tile_rows`` and
         ``tc_rows`` (rows of a tile of the mma.sync and of the tcgen05 tile kernel),
         ``split_keys`` (keys of a tile of the split kernel), ``split_slots`` (CTAs of the
-        split kernel the GPU runs at a time: two an SM),
+        split kernel the GPU runs at a time: as many an SM as the kernel's registers and
+        shared memory allow),
         ``cluster_splits`` (up to so many context splits are merged inside the kernel),
         ``tensor_cores`` (False: the one-warp-per-row kernel runs, which needs no plan)."""
         tma = self.attention_impl in ("auto", "mma") and hd % 64 == 0
         return {"small_rows": 16, "tile_rows": 64, "tc_rows": self._tc_rows.get(hd, 128),
                 "split_keys": 64,
-                "split_slots": 2 * self.sm_count,
+                "split_slots": self._split_ctas_per_sm.get(hd, 2) * self.sm_count,
+                "cluster_slots": 2 * self.sm_count,   # CTAs up to which the splits merge in clusters
                 # most context splits that merge inside the split kernel (a merge kernel
                 # takes over beyond that)
                 "cluster_splits": 8 if tma and os.environ.get(

@@ -31,7 +31,7 @@ class AttentionPlan:
 
 
 def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int = 0,
-                   longest: int = 0) -> int:
+                   longest: int = 0, cluster_slots: int = 0) -> int:
     """Context splits for decoding requests of ``tiles[i]`` key tiles (64 keys) each.
 
     The kernel cuts every request at the same multiples of tiles, the tiles of the step's
@@ -42,7 +42,7 @@ def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int
     CTAs that have tiles times the tiles a CTA walks (plus six tiles' worth of start-up),
     plus what placing the empty CTAs costs, plus the merge's time, which grows with the
     number of parts (measured at batch 1: 16 parts beat 32).  Up to ``cluster_splits``
-    parts are merged inside the split kernel while one round of CTAs holds them all;
+    parts are merged inside the split kernel while ``cluster_slots`` CTAs hold them all;
     beyond that a merge kernel follows, which costs about what two tiles take.  The
     cheapest choice wins; a split is never shorter than 256 keys.
     """
@@ -58,7 +58,7 @@ def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int
         cost = -(-busy // slots) * (per + 6) + 2.0 * (grid - busy) / slots
         if s > 1:
             cost += 0.3 * s
-            if not (cluster_splits and s <= cluster_splits and grid <= slots):
+            if not (cluster_splits and s <= cluster_splits and grid <= (cluster_slots or slots)):
                 cost += 2.0
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
@@ -132,7 +132,8 @@ class GroupedQueryAttention(Mixer):
                 tiles = [-(-c // keys) for c, s in zip(step.ctx_lens, small) if s]
                 n_split = context_splits(tiles, self.n_kv_heads, f["split_slots"],
                                          f.get("cluster_splits", 0),
-                                         longest=-(-step.max_ctx_len // keys))
+                                         longest=-(-step.max_ctx_len // keys),
+                                         cluster_slots=f.get("cluster_slots", 0))
             plan = AttentionPlan(
                 n_tiles=sum(-(-r // f["tile_rows"]) for r in big),
                 n_tiles_tc=sum(-(-r // f["tc_rows"]) for r in big),
