@@ -289,3 +289,42 @@ def test_a_kernels_refusal_raises_in_the_step_that_ran_it(folders):
     with pytest.raises(KernelError, match="token id outside the vocabulary"):
         eng.step()
     eng.model.runtime.ops.check_status()                 # the word was cleared
+
+
+@pytest.mark.parametrize("key, dtype", [("A", "float32"), ("D", "bfloat16")])
+def test_a_repeated_prompt_step_replays_from_a_graph_with_the_same_logits(folders, key, dtype):
+    """Steps with portions of prompts are captured when their shape has come three times and
+    the host was their bound (a tiny model always is): equal portions of several prompts,
+    each beside the same number of decoding requests, give the logits of the step run
+    kernel by kernel, to the bit (the same kernels with the same arguments)."""
+    import torch
+    from mini_llm_stack_b200.engine.batch import Entry
+    from mini_llm_stack_b200.engine.runner import ModelRunner, load_model
+    folder, cfg, w = folders[(key, dtype)]
+    model = load_model(folder, dtype=dtype)
+    runs = {}
+    for graphs in (False, True):
+        runner = ModelRunner(model, num_blocks=64, block_size=16, max_requests=8, cuda_graphs=graphs)
+        gen = torch.Generator().manual_seed(5)
+        rows = []
+        # one request decodes throughout; five others bring a prompt of three portions of 24 each
+        first = [Entry("d", torch.randint(0, cfg["vocab_size"], (9,), generator=gen).tolist(), [8])]
+        runner.reserve(first)
+        rows.append(runner.step(first).clone())
+        for r in range(5):
+            for portion in range(3):
+                toks = torch.randint(0, cfg["vocab_size"], (24,), generator=gen).tolist()
+                e = [Entry("d", [int(rows[-1][0].argmax())], [0]), Entry(f"p{r}", toks, [23])]
+                runner.reserve(e)
+                rows.append(runner.step(e).clone())
+            runner.release(f"p{r}")
+        torch.cuda.synchronize()
+        model.runtime.ops.check_status()
+        runs[graphs] = rows
+        if graphs:
+            captured = [k for k, v in runner._graphs.items() if k != "moved" and isinstance(v, tuple)]
+            assert any(k[0] == (1, 24) for k in captured), captured
+        runner.cache.check()
+    assert len(runs[True]) == len(runs[False]) == 16
+    for a, b in zip(runs[False], runs[True]):
+        assert torch.equal(a, b)
