@@ -268,8 +268,10 @@ def reference_arm(args) -> int:
             clocks.start()
     except Exception:                              # noqa: BLE001
         clocks = None
-    line = arm.run(max(1, args.steps), max(3, args.warmup), args.batch, args.context,
-                   args.layers, not args.no_points)
+    # the arm runs the headline shape (Llama-3-8B): its own defaults where none was given
+    line = arm.run(max(1, args.steps), max(3, args.warmup), args.batch,
+                   args.context or MODEL["max_seq_len"], args.layers or MODEL["n_layers"],
+                   not args.no_points)
     if clocks is not None:
         clocks.stop()
         if "unavailable" not in line:
