@@ -144,6 +144,8 @@ def test_linear_with_float32_weights_in_a_bfloat16_run(rts):
 @pytest.mark.parametrize("m, n, k", [(1, 128, 64), (8, 6144, 4096), (37, 257, 200), (300, 96, 1000),
                                      (64, 1000, 4096), (2048, 512, 1024), (17, 4096, 14336),
                                      (129, 300, 72), (65, 128, 8), (33, 97, 4096),
+                                     # 33 to 48 rows: tiles of 48 columns of tensor memory
+                                     (40, 6144, 4096), (48, 1000, 520),
                                      # row counts whose 128-row tiles do not fill whole rounds of
                                      # CTAs: tiles of 96 + 128 rows, and of 64 + 96
                                      (2, 128256, 128), (5, 22016, 256), (64, 28672, 64),
@@ -170,7 +172,8 @@ def test_linear_bf16(rts, m, n, k, out_dtype, impl):
     assert (out.float() - want).abs().max().item() <= tol * scale + 1e-6
 
 
-@pytest.mark.parametrize("m, n, k", [(1, 4096, 14336), (8, 4096, 4096), (33, 1000, 4104), (64, 96, 2048)])
+@pytest.mark.parametrize("m, n, k", [(1, 4096, 14336), (8, 4096, 4096), (33, 1000, 4104), (64, 96, 2048),
+                                     (48, 4096, 4096)])
 def test_product_left_as_parts_is_summed_by_the_next_norm(rts, m, n, k):
     """A product that only feeds the residual stream keeps its K-parts; add_rmsnorm
     adds them up, for all rows and for chosen rows, and the buffer is lent once."""
@@ -209,6 +212,7 @@ def test_product_left_as_parts_is_summed_by_the_next_norm(rts, m, n, k):
 
 
 @pytest.mark.parametrize("m, inter, k", [(1, 14336, 4096), (8, 176, 64), (64, 256, 96), (33, 4096, 4096),
+                                         (41, 1008, 512), (48, 14336, 4096),
                                          (8, 11008, 128), (3, 10000, 64),
                                           (300, 272, 200), (2048, 1024, 512), (129, 14336, 1024),
                                           # two tiles after three whole rounds, cut along K
