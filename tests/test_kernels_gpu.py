@@ -550,6 +550,24 @@ def test_attention_mixed_batch(rts, dtype, heads, kv, hd, block):
 
 
 @pytest.mark.parametrize("rows", [128, 256])
+@pytest.mark.parametrize("heads, kv, hd, block", [(6, 2, 64, 8), (6, 1, 128, 32), (5, 1, 64, 16)])
+def test_prompt_attention_with_groups_that_do_not_divide_a_row_tile(rts, rows, heads, kv, hd, block):
+    """Three, five or six query heads a kv head: a tile of 128 rows then ends inside a token's
+    heads, and a chain's last token differs from row to row."""
+    ops = rts[torch.bfloat16].ops
+    case = AttnCase(rts[torch.bfloat16], heads, kv, hd, block, [333, 130, 700, 90], [70, 130, 211, 43],
+                    seed=17 + heads)
+    ops.set_attention_rows(hd, rows)
+    try:
+        got = case.run()
+    finally:
+        ops.set_attention_rows(hd, 0)
+    ops.check_status()
+    want = case.want()
+    assert (got - want).abs().max().item() <= attn_tol(torch.bfloat16, 700) * want.abs().max().item()
+
+
+@pytest.mark.parametrize("rows", [128, 256])
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("window", [None, 200])
 def test_prompt_attention_as_two_row_tiles_and_as_two_key_halves(rts, rows, hd, window):
