@@ -111,6 +111,7 @@ class ModelRunner:
         # MLS_B200_PROMPT_GRAPHS=0: only steps of single decoded tokens replay from graphs
         self.prompt_graphs = os.environ.get("MLS_B200_PROMPT_GRAPHS", "1") != "0"
         self._graphs: dict = {}
+        self._capture_stream = None
         self.runtime = model.runtime
         cfg = model.config
         self.cache = CacheManager(
@@ -218,9 +219,7 @@ class ModelRunner:
                     return self.model.forward(ctx, self.handles)
                 return seen.timed(lambda: self.model.forward(ctx, self.handles))
             before = (ops.launches, ops.library_launches)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, self.handles)
+            graph, logits = self._capture(lambda: self.model.forward(ctx, self.handles))
             entry = (graph, logits, ops.launches - before[0], ops.library_launches - before[1])
         self._keep(key, entry)
         graph, logits, own, lib = entry
@@ -228,6 +227,27 @@ class ModelRunner:
         ops.launches += own
         ops.library_launches += lib
         return logits
+
+    def _capture(self, forward):
+        """Record what ``forward`` launches into a CUDA graph, on a side stream that waits
+        for the current one.  (Without
+        the collector run, device-wide wait and cache flush of ``torch.cuda.graph``, which
+        made a capture cost 25-55 ms: a serving run captures dozens of step shapes.)"""
+        device = self.runtime.device
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device)
+        current = torch.cuda.current_stream(device)
+        side = self._capture_stream
+        side.wait_stream(current)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            try:
+                out = forward()
+            finally:
+                graph.capture_end()
+        current.wait_stream(side)
+        return graph, out
 
     def _keep(self, key, entry) -> None:
         self._graphs[key] = entry
