@@ -291,7 +291,8 @@ def test_a_kernels_refusal_raises_in_the_step_that_ran_it(folders):
     eng.model.runtime.ops.check_status()                 # the word was cleared
 
 
-@pytest.mark.parametrize("key, dtype", [("A", "float32"), ("D", "bfloat16")])
+@pytest.mark.parametrize("key, dtype", [("A", "float32"), ("D", "bfloat16"), ("C", "float32"),
+                                        ("C", "bfloat16"), ("E", "bfloat16")])
 def test_a_repeated_prompt_step_replays_from_a_graph_with_the_same_logits(folders, key, dtype):
     """Steps with portions of prompts are captured when their shape has come three times and
     the host was their bound (a tiny model always is): equal portions of several prompts,
