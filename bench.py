@@ -486,7 +486,8 @@ def main() -> int:
 
     mark0 = clocks.mark()
     # the decode line first: the prompt steps that follow run under the power cap, and decode
-    # steps timed after them came out 1.2 % slower (4.46 against 4.41 ms) in runs of either order
+    # steps timed right after them came out 1.2 % slower (4.46 against 4.41 ms; a second's pause
+    # between the two brought the 4.41 ms back)
     ms, launches, mean_ctx = decode_run(args.batch, warmup, steps)
     # the median of single steps: the first steps of a process run at boost clocks,
     # later ones under the power cap
