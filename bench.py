@@ -485,17 +485,10 @@ def main() -> int:
         return ms, launches, mean_ctx
 
     mark0 = clocks.mark()
-    # the decode line first: the prompt steps that follow run under the power cap, and decode
-    # steps timed right after them came out 1.2 % slower (4.46 against 4.41 ms; a second's pause
-    # between the two brought the 4.41 ms back)
+    # the decode line and the decode points first: the prompt steps that follow run under the
+    # power cap, and decode steps timed right after them came out 1.2 % slower (4.46 against
+    # 4.41 ms at batch 8, 6 % at batch 1; a second's pause between the two brought the times back)
     ms, launches, mean_ctx = decode_run(args.batch, warmup, steps)
-    # the median of single steps: the first steps of a process run at boost clocks,
-    # later ones under the power cap
-    prefill_ms = sorted(timed(prefill_once, 1 if i else 3, 1)[0] for i in range(9))[4]
-    pf = prefill_flops(raw, args.layers, PREFILL_TOKENS)
-    prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
-               "ms": round(prefill_ms, 3),
-               "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     value = args.batch / ms * 1e3
     step_bytes = weight_bytes(raw, args.layers) + args.batch * mean_ctx * kv_bytes_per_token(
         raw, args.layers)
@@ -513,6 +506,14 @@ def main() -> int:
                 pms, _, _ = decode_run(b, 3, max(8, steps // 4), end=1024)
                 points[f"decode_b{b}_ctx1024"] = round(b / pms * 1e3, 1)
 
+    # the median of single steps: the first steps of a process run at boost clocks,
+    # later ones under the power cap
+    prefill_ms = sorted(timed(prefill_once, 1 if i else 3, 1)[0] for i in range(9))[4]
+    pf = prefill_flops(raw, args.layers, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 3),
+               "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    if not args.no_points:
         def prefill_in_four():                   # the same prompt in four portions of 512
             toks = rand_tokens(PREFILL_TOKENS)
             for at in range(0, PREFILL_TOKENS, 512):

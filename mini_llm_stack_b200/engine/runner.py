@@ -173,7 +173,7 @@ class ModelRunner:
 
     GRAPHS_KEPT = 48             # captured steps kept; the oldest goes first
     PROMPT_SHAPE_SEEN = 3        # a step with portions is captured when its shape comes this often
-    HOST_BOUND = 0.5             # ... and issuing it took the host this share of its time on the GPU
+    HOST_BOUND = 0.25            # ... and issuing it took the host this share of its time on the GPU
 
     def _may_replay(self, ctx) -> bool:
         """A step of single decoded tokens, all wanted, of a model whose parts all agree
@@ -194,9 +194,10 @@ class ModelRunner:
         first step of a kind runs eagerly (which sizes every buffer), the second is
         captured, later ones replay.  A step with portions of prompts, whose shape may
         never come again, is captured when it has come ``PROMPT_SHAPE_SEEN`` times and
-        the host was what it waited for: issuing its kernels one by one took at least
-        ``HOST_BOUND`` of the time the GPU spent on them (small models, short portions).
-        A large step gains nothing from a graph.
+        the host had a part in its time: issuing its kernels one by one took at least
+        ``HOST_BOUND`` of the time the GPU spent on them (small models, portions of a few
+        hundred tokens: the gaps between their kernels go away).  A large step gains nothing
+        from a graph.
         """
         ops = self.runtime.ops
         moved = (ops.generation, self.builder.generation)
