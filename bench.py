@@ -506,8 +506,11 @@ def main() -> int:
                 pms, _, _ = decode_run(b, 3, max(8, steps // 4), end=1024)
                 points[f"decode_b{b}_ctx1024"] = round(b / pms * 1e3, 1)
 
-    # the median of single steps: the first steps of a process run at boost clocks,
-    # later ones under the power cap
+    # The prompt steps start from a rested GPU, as the decode line did: what ran before leaves
+    # its mark for about a second (clocks under the power cap).  The median of single steps:
+    # the first run at boost clocks, later ones under the power cap.
+    torch.cuda.synchronize()
+    time.sleep(1.0)
     prefill_ms = sorted(timed(prefill_once, 1 if i else 3, 1)[0] for i in range(9))[4]
     pf = prefill_flops(raw, args.layers, PREFILL_TOKENS)
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
