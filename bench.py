@@ -538,6 +538,8 @@ def main() -> int:
             for _ in range(args.batch)]
     while any(r.remaining > 1 or not r.generated for r in reqs):
         engine.step()                            # prompts in portions, untimed
+    torch.cuda.synchronize()
+    time.sleep(1.0)                              # the prompts' mark on the clocks fades, as above
     for _ in range(warmup):
         engine.step()
     assert len(engine.running) == args.batch
