@@ -764,6 +764,32 @@ attention_split_tma_kernel(const Params P, const Fused F,
         }
         return;
     }
+    // fused rotation (single decoded tokens): the position, its rows of the angle tables and
+    // the new token's slot are the step's own input and are read while the projection before
+    // this kernel may still run
+    const bool fused = F.parts != nullptr;
+    constexpr int ROT_HALF = HD / 2, ROT_QPH = ROT_HALF / 4, ROT_ITERS = (16 * ROT_QPH + 127) / 128;
+    float4 rot_cos[ROT_ITERS], rot_sin[ROT_ITERS];
+    int rot_slot = -1;
+    if (fused && n_tiles > 0) {
+        int pos = F.positions[tok0];
+        if (pos < 0 || pos >= F.max_pos || q_len != 1) {
+            if (threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_POSITION);
+            pos = pos < 0 ? 0 : (pos >= F.max_pos ? F.max_pos - 1 : pos);
+        }
+        const float* cr = F.cos_t + (size_t)pos * ROT_HALF;
+        const float* sr = F.sin_t + (size_t)pos * ROT_HALF;
+#pragma unroll
+        for (int k = 0; k < ROT_ITERS; ++k) {
+            const int u = threadIdx.x + k * 128;
+            if (u < 16 * ROT_QPH) {
+                const int c = u % ROT_QPH;
+                rot_cos[k] = *reinterpret_cast<const float4*>(cr + c * 4);
+                rot_sin[k] = *reinterpret_cast<const float4*>(sr + c * 4);
+            }
+        }
+        if (F.writes && t_end == tiles_all) rot_slot = F.slot_map[tok0];
+    }
     chain_wait();
 
     // --------------------------------------------------------------------- consumers
@@ -779,23 +805,18 @@ attention_split_tma_kernel(const Params P, const Fused F,
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
     uint32_t qf[HD / 16][4];
 
-    // fused rotation (single decoded tokens): this CTA's queries from the projection's parts,
-    // and, in the CTA whose tiles end at the new token, the new key and value
-    const bool fused = F.parts != nullptr;
+    // this CTA's queries from the projection's parts, and, in the CTA whose tiles end at the
+    // new token, the new key and value
     const bool owns_new = fused && F.writes && n_tiles > 0 && t_end == tiles_all;
     uint2 new_kv[2] = {make_uint2(0u, 0u), make_uint2(0u, 0u)};     // this thread's share of them
     if (fused && n_tiles > 0) {
-        constexpr int half = HD / 2, qph = half / 4;
-        int pos = F.positions[tok0];
-        if (pos < 0 || pos >= F.max_pos || q_len != 1) {
-            if (threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_POSITION);
-            pos = pos < 0 ? 0 : (pos >= F.max_pos ? F.max_pos - 1 : pos);
-        }
-        const float* cr = F.cos_t + (size_t)pos * half;
-        const float* sr = F.sin_t + (size_t)pos * half;
+        constexpr int half = ROT_HALF, qph = ROT_QPH;
         const size_t width = (size_t)(P.n_heads + 2 * P.n_kv) * HD;
         const size_t row_at = (size_t)tok0 * width;
-        for (int u = threadIdx.x; u < 16 * qph; u += 128) {
+#pragma unroll
+        for (int k = 0; k < ROT_ITERS; ++k) {
+            const int u = threadIdx.x + k * 128;
+            if (u >= 16 * qph) break;
             const int g = u / qph, c = u - g * qph;
             uint2 w1 = make_uint2(0u, 0u), w2 = w1;
             if (g < rows) {
@@ -803,9 +824,7 @@ attention_split_tma_kernel(const Params P, const Fused F,
                 const size_t at[2] = {row_at + col, row_at + col + half};
                 float4 x[2], o1, o2;
                 sum_parts4_of<2, 8>(F.parts, at, F.n_parts, (size_t)F.part_stride, x);
-                rotate_half4(round_bf16(x[0]), round_bf16(x[1]),
-                             *reinterpret_cast<const float4*>(cr + c * 4),
-                             *reinterpret_cast<const float4*>(sr + c * 4), o1, o2);
+                rotate_half4(round_bf16(x[0]), round_bf16(x[1]), rot_cos[k], rot_sin[k], o1, o2);
                 w1 = pack_bf16x4(o1);
                 w2 = pack_bf16x4(o2);
             }
@@ -817,7 +836,7 @@ attention_split_tma_kernel(const Params P, const Fused F,
         if (owns_new) {
             // threads 0 .. qph-1: four rotated pairs of the key each; the next HD / 4: four
             // values of the value each.  Into the cache now, into the tile when it has landed.
-            const int slot = F.slot_map[tok0];
+            const int slot = rot_slot;
             const long long pool_slots = P.n_pages * P.block_size;
             const bool slot_ok = slot >= 0 && slot < pool_slots;
             if (!slot_ok && threadIdx.x == 0 && P.status) atomicOr(P.status, MLS_STATUS_BAD_SLOT);
@@ -830,9 +849,8 @@ attention_split_tma_kernel(const Params P, const Fused F,
                 const size_t at[2] = {row_at + col, row_at + col + half};
                 float4 x[2], o1, o2;
                 sum_parts4_of<2, 8>(F.parts, at, F.n_parts, (size_t)F.part_stride, x);
-                rotate_half4(round_bf16(x[0]), round_bf16(x[1]),
-                             *reinterpret_cast<const float4*>(cr + u * 4),
-                             *reinterpret_cast<const float4*>(sr + u * 4), o1, o2);
+                // thread u < qph took chunk u of the angles in its first round above
+                rotate_half4(round_bf16(x[0]), round_bf16(x[1]), rot_cos[0], rot_sin[0], o1, o2);
                 new_kv[0] = pack_bf16x4(o1);
                 new_kv[1] = pack_bf16x4(o2);
                 if (slot_ok) {
