@@ -459,6 +459,8 @@ def main() -> int:
         """Device time of one decode step with ``batch`` requests that end at ``end``
         (the context length by default); every row sampled at ``temperature`` if that
         is positive, else by arg max."""
+        torch.cuda.synchronize()
+        time.sleep(1.0)                         # every point starts from a GPU at rest (see below)
         start = (end or ctx) - (n_warm + n_timed)
         ids = [f"d{batch}_{i}" for i in range(batch)]
         for r in ids:
