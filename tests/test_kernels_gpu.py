@@ -646,6 +646,28 @@ def test_far_key_at_the_full_context_with_the_8b_heads(rts, far, ctx, q_len):
     assert (got[visible] - mark).abs().max().item() < 3e-2
 
 
+@pytest.mark.parametrize("far, q_len", [(5, 1), (33001, 1), (17, 200), (39000, 1100)])
+def test_far_key_in_a_context_of_forty_thousand(rts, far, q_len):
+    """A context past 2^15 keys and 2,048 pages (positions, page numbers and tile counts
+    that no longer fit 15 or 16 bits): one decoded token, a short portion and a long one
+    each have to find the one key that stands out."""
+    ctx = 40000
+    case = AttnCase(rts[torch.bfloat16], 8, 2, 128, 16, [ctx], [q_len], seed=9)
+    q, k, v = case.q[0], case.k[0], case.v[0]
+    k.mul_(0.05)
+    direction = torch.ones(128, dtype=q.dtype, device=DEV)
+    q[:] = direction * 3
+    k[:, far] = direction * 3                      # 9 * 128 / 11.3 = 102 above all others
+    got = case.run()
+    rts[torch.bfloat16].ops.check_status()
+    mark = v[:, far].float().cpu().repeat_interleave(4, dim=0).reshape(1, -1)
+    visible = torch.arange(ctx - q_len, ctx) >= far
+    assert bool(visible.any())
+    assert (got[visible] - mark).abs().max().item() < 3e-2
+    if not bool(visible.all()):                    # rows before the key: an ordinary average
+        assert got[~visible].abs().max().item() < 1.0
+
+
 @pytest.mark.parametrize("far, ctx, q_len", [(55, 4096, 1), (2049, 4096, 700), (4000, 4096, 97)])
 def test_far_key_with_heads_of_64(rts, far, ctx, q_len):
     """The same with 32 query heads over 8 kv heads of 64 (the Llama-3.2-1B geometry): the
