@@ -788,8 +788,6 @@ int launch(const GemmParams& p, const void* a, const void* b, int ctas_per_sm,
 
 // How a product on pairs of CTAs cuts the tiles of its last round (see pair_unit): so many
 // parts that every pair gets one, at least four k-blocks each.  parts <= 1: nothing is cut.
-// How a product on pairs of CTAs cuts the tiles of its last round (see pair_unit): so many
-// parts that every pair gets one, at least four k-blocks each.  parts <= 1: nothing is cut.
 //
 // When it pays (measured, Llama-3-8B products): at full occupancy the pairs are bound by what
 // all SMs together draw from L2, not by rounds, so a last round of a few tiles runs faster
